@@ -1,0 +1,696 @@
+// Host side of libb200gemm.so: argument validation, tile-config selection, TMA tensor-map
+// construction and kernel launches behind the C ABI declared in include/b200gemm.h.
+//
+// Tile-config selection replaces the reference's compile-time traits structs
+// (opus_gemm/gemm_a8w8_8wave.cc:36-96, block_scale_gemm/gemm_a8w8_blockscale_common.h:28-84,
+// opus_fmm/flatmm_a8w8_gfx950.cc:36-104) with a run-time choice from a small static table.
+#include "../../include/b200gemm.h"
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "aux_kernels.cuh"
+#include "decode_sm100.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using namespace b200;
+
+std::atomic<uint64_t> g_launches{0};
+thread_local int g_last_cuda = 0;
+
+__device__ int g_status_word;
+
+#define CU_TRY(expr)                                   \
+    do {                                               \
+        cudaError_t e_ = (expr);                       \
+        if (e_ != cudaSuccess) {                       \
+            g_last_cuda = static_cast<int>(e_);        \
+            return B200_ERR_CUDA;                      \
+        }                                              \
+    } while (0)
+
+// ---- per-device state ------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool init = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status_ptr = nullptr;
+    // cached buffers of b200_gemm_a8w8_host
+    void* buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int device_state(DeviceState** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        g_last_cuda = static_cast<int>(e);
+        return B200_ERR_NO_DEVICE;
+    }
+    if (dev < 0 || dev >= kMaxDevices) return B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[dev];
+    if (!s.init) {
+        cudaDeviceProp prop;
+        CU_TRY(cudaGetDeviceProperties(&prop, dev));
+        s.sm_count = prop.multiProcessorCount;
+        s.cc_major = prop.major;
+        if (prop.major != 10) return B200_ERR_NO_DEVICE;
+        void* sym = nullptr;
+        CU_TRY(cudaGetSymbolAddress(&sym, g_status_word));
+        s.status_ptr = static_cast<int*>(sym);
+        CU_TRY(cudaMemset(s.status_ptr, 0, sizeof(int)));
+        if (!g_encode) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            CU_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+            if (q != cudaDriverEntryPointSuccess || !fn) return B200_ERR_NO_DEVICE;
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        s.init = true;
+    }
+    *out = &s;
+    return B200_OK;
+}
+
+// u8 tensor map of rank `rank`; dims/strides innermost first, strides[i] = byte stride of dim i+1
+int make_tmap(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+              const uint32_t* box, CUtensorMapSwizzle swz) {
+    cuuint64_t gd[5], gs[4];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        gd[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+    }
+    for (int i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gd,
+                          gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda = 100000 + static_cast<int>(r);
+        return B200_ERR_CUDA;
+    }
+    return B200_OK;
+}
+
+// row-major u8 [batch][rows][K] with a 128-byte-swizzled box of 128 (K) x box_rows
+int make_rowmajor_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t k, int64_t ld, int64_t batch,
+                       int64_t batch_stride, uint32_t box_rows) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(rows), static_cast<uint64_t>(batch)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(ld),
+                                 static_cast<uint64_t>(batch > 1 ? batch_stride : ld * rows)};
+    const uint32_t box[3] = {128, box_rows, 1};
+    return make_tmap(tm, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// flat image [N/16][K/16][256 B] viewed as (256 B, slab, k-chunk, batch): a box {256, rows/16, 8, 1}
+// lands in shared memory as [k-chunk][slab][256 B]
+int make_flat_tmap(CUtensorMap* tm, const void* base, int64_t n, int64_t k, int64_t batch, int64_t batch_stride,
+                   uint32_t box_rows) {
+    const uint64_t dims[4] = {256, static_cast<uint64_t>(n / 16), static_cast<uint64_t>(k / 16),
+                              static_cast<uint64_t>(batch)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(k * 16), 256,
+                                 static_cast<uint64_t>(batch > 1 ? batch_stride : n * k)};
+    const uint32_t box[4] = {256, box_rows / 16, 8, 1};
+    return make_tmap(tm, base, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// ---- validation and config selection -----------------------------------------------------------
+struct Plan {
+    int tile;        // b200_tile_hint value actually used
+    int mt;          // decode token block
+    int splits;      // decode K splits
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
+    if (!a || !a->ptr_a || !a->ptr_b || !a->ptr_c) return B200_ERR_BAD_ARG;
+    if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return B200_ERR_BAD_ARG;
+    if (a->scale_mode < 0 || a->scale_mode > 3 || a->b_layout < 0 || a->b_layout > 1 || a->out_dtype < 0 ||
+        a->out_dtype > 1 || a->tile_hint < 0 || a->tile_hint > 6)
+        return B200_ERR_BAD_ARG;
+    if (a->m > 0x7FFFFFFF || a->n > 0x7FFFFFFF || a->k > 0x7FFFFFFF || a->batch > 65535) return B200_ERR_TOO_LARGE;
+    if (a->stride_a < a->k || a->stride_c < a->n) return B200_ERR_BAD_ARG;
+    // TMA: 16-byte aligned bases and row pitches
+    if (!aligned16(a->ptr_a) || !aligned16(a->ptr_b)) return B200_ERR_UNSUPPORTED;
+    if (a->stride_a % 16 != 0 || a->k % 16 != 0) return B200_ERR_UNSUPPORTED;
+    if (a->batch > 1 && (a->stride_a_batch % 16 != 0 || a->stride_b_batch % 16 != 0)) return B200_ERR_UNSUPPORTED;
+    if (a->b_layout == B200_B_NK_ROWMAJOR) {
+        if (a->stride_b < a->k) return B200_ERR_BAD_ARG;
+        if (a->stride_b % 16 != 0) return B200_ERR_UNSUPPORTED;
+    } else {
+        if (a->n % 16 != 0 || a->k % 128 != 0) return B200_ERR_UNSUPPORTED;   // flat needs whole 16x16 blocks
+    }
+    if (a->scale_mode == B200_SCALE_BLOCK) {
+        if (!a->ptr_sfa || !a->ptr_sfb) return B200_ERR_BAD_ARG;
+        // GROUP_M/N/K = 1/128/128 check of gemm_a8w8_blockscale_host.cc:183
+        if (a->n % 128 != 0 || a->k % 128 != 0) return B200_ERR_UNSUPPORTED;
+        if (a->stride_sfa < a->m || a->stride_sfb < a->k / 128) return B200_ERR_BAD_ARG;
+    }
+    if (a->scale_mode == B200_SCALE_MX) {
+        if (!a->ptr_sfa || !a->ptr_sfb) return B200_ERR_BAD_ARG;
+        if (a->k % 128 != 0) return B200_ERR_UNSUPPORTED;
+        if (!aligned16(a->ptr_sfa) || !aligned16(a->ptr_sfb)) return B200_ERR_UNSUPPORTED;
+        if (a->batch > 1 && (a->stride_sfa_batch % 16 != 0 || a->stride_sfb_batch % 16 != 0)) return B200_ERR_UNSUPPORTED;
+    }
+
+    Plan pl{B200_TILE_128x128, 0, 1};
+    const int64_t kblocks = (a->k + 127) / 128;
+    const bool decode_ok = a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
+    int hint = a->tile_hint;
+    if (hint == B200_TILE_DECODE && !decode_ok) return B200_ERR_UNSUPPORTED;
+    if (hint == B200_TILE_PAIR_256x256 || hint == B200_TILE_PAIR_256x128 || hint == B200_TILE_128x64)
+        return B200_ERR_UNSUPPORTED;
+    if (hint == B200_TILE_AUTO) {
+        if (decode_ok) hint = B200_TILE_DECODE;
+        else if (a->scale_mode == B200_SCALE_MX) hint = B200_TILE_128x128;
+        else {
+            const int64_t t256 = ((a->m + 127) / 128) * ((a->n + 255) / 256) * a->batch;
+            hint = (t256 >= sm_count) ? B200_TILE_128x256 : B200_TILE_128x128;
+        }
+    }
+    if (hint == B200_TILE_128x256 && a->scale_mode == B200_SCALE_MX) return B200_ERR_UNSUPPORTED;
+    pl.tile = hint;
+    if (hint == B200_TILE_DECODE) {
+        pl.mt = a->m <= 16 ? 16 : (a->m <= 32 ? 32 : 64);
+        // K splits: fill the machine when there are fewer weight panels than SMs, and keep the
+        // per-CTA scale staging within its shared-memory budget
+        const int64_t tiles = ((a->n + 127) / 128) * a->batch;
+        int splits = 1;
+        while (tiles * splits * 2 <= sm_count && splits * 2 <= kblocks && splits < 16) splits *= 2;
+        if (a->scale_mode == B200_SCALE_BLOCK) {
+            const int64_t cap = (34 * 1024 / 4);
+            while (((kblocks + splits - 1) / splits) * (pl.mt + 1) > cap) {
+                splits *= 2;
+                if (splits > kblocks) return B200_ERR_TOO_LARGE;
+            }
+        }
+        pl.splits = splits;
+    }
+    if (plan) *plan = pl;
+    return B200_OK;
+}
+
+template <class Kernel>
+int set_smem(Kernel kernel, int bytes) {
+    CU_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    return B200_OK;
+}
+
+template <int BN, int MODE, int BL>
+int launch_gemm(const GemmParams& p, int grid, cudaStream_t st) {
+    using Cfg = GemmCfg<BN, MODE, BL>;
+    auto kernel = gemm_a8w8_sm100_kernel<Cfg>;
+    int rc = set_smem(kernel, Cfg::SMEM_BYTES);
+    if (rc) return rc;
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+
+template <int MT, int MODE, int BL>
+int launch_decode(const DecodeParams& p, int grid, cudaStream_t st) {
+    using Cfg = DecodeCfg<MT, MODE, BL>;
+    auto kernel = decode_a8w8_sm100_kernel<Cfg>;
+    int rc = set_smem(kernel, Cfg::SMEM_BYTES);
+    if (rc) return rc;
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+
+template <int MODE, int BL>
+int launch_decode_mt(int mt, const DecodeParams& p, int grid, cudaStream_t st) {
+    switch (mt) {
+        case 16: return launch_decode<16, MODE, BL>(p, grid, st);
+        case 32: return launch_decode<32, MODE, BL>(p, grid, st);
+        default: return launch_decode<64, MODE, BL>(p, grid, st);
+    }
+}
+
+// split-K scratch of the decode path, one per device, grown on demand
+struct Scratch {
+    float* ptr = nullptr;
+    size_t cap = 0;
+};
+Scratch g_scratch[kMaxDevices];
+
+int run_decode(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
+    DecodeParams p;
+    std::memset(&p, 0, sizeof(p));
+    int rc;
+    if (a->b_layout == B200_B_NK_ROWMAJOR)
+        rc = make_rowmajor_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, 128);
+    else
+        rc = make_flat_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, 128);
+    if (rc) return rc;
+    rc = make_rowmajor_tmap(&p.tmap_x, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, pl.mt);
+    if (rc) return rc;
+    p.c = a->ptr_c;
+    p.sfa = static_cast<const float*>(a->ptr_sfa);
+    p.sfb = static_cast<const float*>(a->ptr_sfb);
+    p.scale_a = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_a : nullptr;
+    p.scale_b = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_b : nullptr;
+    p.ldc = a->stride_c;
+    p.c_batch = a->stride_c_batch;
+    p.sfa_stride = a->stride_sfa;
+    p.sfb_stride = a->stride_sfb;
+    p.sfa_batch = a->stride_sfa_batch;
+    p.sfb_batch = a->stride_sfb_batch;
+    p.m = static_cast<int>(a->m);
+    p.n = static_cast<int>(a->n);
+    p.k = static_cast<int>(a->k);
+    p.batch = static_cast<int>(a->batch);
+    p.tiles_n = static_cast<int>((a->n + 127) / 128);
+    p.kblocks = static_cast<int>((a->k + 127) / 128);
+    p.splits = pl.splits;
+    p.kb_per_split = (p.kblocks + pl.splits - 1) / pl.splits;
+    p.out_dtype = a->out_dtype;
+    p.status = ds->status_ptr;
+    if (pl.splits > 1) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const size_t need = static_cast<size_t>(pl.splits) * a->batch * a->m * a->n * sizeof(float);
+        std::lock_guard<std::mutex> lk(g_mu);
+        Scratch& s = g_scratch[dev];
+        if (s.cap < need) {
+            if (s.ptr) CU_TRY(cudaFree(s.ptr));
+            s.ptr = nullptr;
+            s.cap = 0;
+            CU_TRY(cudaMalloc(&s.ptr, need));
+            s.cap = need;
+        }
+        p.partial = s.ptr;
+    }
+    const int grid = p.tiles_n * p.batch * pl.splits;
+    const bool block = a->scale_mode == B200_SCALE_BLOCK;
+    if (a->b_layout == B200_B_NK_ROWMAJOR)
+        rc = block ? launch_decode_mt<MODE_BLOCK, BL_NK>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_NK>(pl.mt, p, grid, st);
+    else
+        rc = block ? launch_decode_mt<MODE_BLOCK, BL_FLAT>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_FLAT>(pl.mt, p, grid, st);
+    if (rc) return rc;
+    if (pl.splits > 1) {
+        const long long per_split = static_cast<long long>(a->batch) * a->m * a->n;
+        const int threads = 256;
+        const unsigned blocks = static_cast<unsigned>((per_split + threads - 1) / threads);
+        decode_splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.partial, a->ptr_c, pl.splits, per_split, p.m, p.n,
+                                                               p.ldc, p.c_batch, p.out_dtype);
+        CU_TRY(cudaGetLastError());
+        g_launches.fetch_add(1);
+    }
+    return B200_OK;
+}
+
+int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
+    const int BN = pl.tile == B200_TILE_128x256 ? 256 : 128;
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    int rc = make_rowmajor_tmap(&p.tmap_a, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, 128);
+    if (rc) return rc;
+    if (a->b_layout == B200_B_NK_ROWMAJOR)
+        rc = make_rowmajor_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, BN);
+    else
+        rc = make_flat_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, BN);
+    if (rc) return rc;
+    p.c = a->ptr_c;
+    p.sfa = static_cast<const float*>(a->ptr_sfa);
+    p.sfb = static_cast<const float*>(a->ptr_sfb);
+    p.scale_a = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_a : nullptr;
+    p.scale_b = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_b : nullptr;
+    p.ldc = a->stride_c;
+    p.c_batch = a->stride_c_batch;
+    p.m = static_cast<int>(a->m);
+    p.n = static_cast<int>(a->n);
+    p.k = static_cast<int>(a->k);
+    p.batch = static_cast<int>(a->batch);
+    p.tiles_m = static_cast<int>((a->m + 127) / 128);
+    p.tiles_n = static_cast<int>((a->n + BN - 1) / BN);
+    const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batch;
+    if (total > 0x7FFFFFFF) return B200_ERR_TOO_LARGE;
+    p.tiles_total = static_cast<int>(total);
+    p.kblocks = static_cast<int>((a->k + 127) / 128);
+    p.out_dtype = a->out_dtype;
+    p.status = ds->status_ptr;
+    if (a->scale_mode == B200_SCALE_MX) {
+        // atoms [K/128][rows/128][512 B]: strides in atoms, batch strides in bytes
+        p.sfa_stride = (a->m + 127) / 128;
+        p.sfb_stride = (a->n + 127) / 128;
+        p.sfa_batch = a->stride_sfa_batch;
+        p.sfb_batch = a->stride_sfb_batch;
+    } else {
+        p.sfa_stride = a->stride_sfa;
+        p.sfb_stride = a->stride_sfb;
+        p.sfa_batch = a->stride_sfa_batch;
+        p.sfb_batch = a->stride_sfb_batch;
+    }
+    const int grid = p.tiles_total < ds->sm_count ? p.tiles_total : ds->sm_count;
+    const bool flat = a->b_layout == B200_B_FLAT_16x16;
+    switch (a->scale_mode) {
+        case B200_SCALE_BLOCK:
+            if (BN == 256) return flat ? launch_gemm<256, MODE_BLOCK, BL_FLAT>(p, grid, st) : launch_gemm<256, MODE_BLOCK, BL_NK>(p, grid, st);
+            return flat ? launch_gemm<128, MODE_BLOCK, BL_FLAT>(p, grid, st) : launch_gemm<128, MODE_BLOCK, BL_NK>(p, grid, st);
+        case B200_SCALE_MX:
+            return flat ? launch_gemm<128, MODE_MX, BL_FLAT>(p, grid, st) : launch_gemm<128, MODE_MX, BL_NK>(p, grid, st);
+        default:
+            if (BN == 256) return flat ? launch_gemm<256, MODE_ACC, BL_FLAT>(p, grid, st) : launch_gemm<256, MODE_ACC, BL_NK>(p, grid, st);
+            return flat ? launch_gemm<128, MODE_ACC, BL_FLAT>(p, grid, st) : launch_gemm<128, MODE_ACC, BL_NK>(p, grid, st);
+    }
+}
+
+// ---- host generators ----------------------------------------------------------------------------
+inline uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+inline uint64_t stream_key(uint64_t seed, uint32_t tensor_id) {
+    return mix64(seed ^ (static_cast<uint64_t>(tensor_id) << 32) ^ 0xA8F8A8F8ull);
+}
+inline uint64_t draw64(uint64_t key, uint64_t idx) { return mix64(key + idx * 0xD1342543DE82EF95ull); }
+
+int ensure(DeviceState* ds, int slot, size_t bytes) {
+    if (ds->cap[slot] >= bytes) return B200_OK;
+    if (ds->buf[slot]) CU_TRY(cudaFree(ds->buf[slot]));
+    ds->buf[slot] = nullptr;
+    ds->cap[slot] = 0;
+    const size_t want = bytes + (bytes >> 3) + 256;
+    CU_TRY(cudaMalloc(&ds->buf[slot], want));
+    ds->cap[slot] = want;
+    return B200_OK;
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+int b200_gemm_check(const b200_gemm_args* args, int32_t* chosen_tile) {
+    Plan pl;
+    int sms = 148;
+    int rc = validate(args, sms, &pl);
+    if (rc == B200_OK && chosen_tile) *chosen_tile = pl.tile;
+    return rc;
+}
+
+int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream) {
+    Plan pl;
+    int rc = validate(args, 148, &pl);
+    if (rc) return rc;
+    DeviceState* ds = nullptr;
+    rc = device_state(&ds);
+    if (rc) return rc;
+    rc = validate(args, ds->sm_count, &pl);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (pl.tile == B200_TILE_DECODE) return run_decode(args, pl, ds, st);
+    return run_gemm(args, pl, ds, st);
+}
+
+int b200_gemm_a8w8_simple(const b200_gemm_args* a, void* cuda_stream) {
+    if (!a || !a->ptr_a || !a->ptr_b || !a->ptr_c) return B200_ERR_BAD_ARG;
+    if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0 || a->m > 65535 * 1LL * 65535 || a->batch > 65535) return B200_ERR_BAD_ARG;
+    if (a->m > 65535) return B200_ERR_TOO_LARGE;
+    if ((a->scale_mode == B200_SCALE_BLOCK || a->scale_mode == B200_SCALE_MX) && (!a->ptr_sfa || !a->ptr_sfb)) return B200_ERR_BAD_ARG;
+    SimpleParams p;
+    p.a = static_cast<const uint8_t*>(a->ptr_a);
+    p.b = static_cast<const uint8_t*>(a->ptr_b);
+    p.c = a->ptr_c;
+    p.sfa = a->ptr_sfa;
+    p.sfb = a->ptr_sfb;
+    p.scale_a = a->ptr_scale_a;
+    p.scale_b = a->ptr_scale_b;
+    p.m = a->m; p.n = a->n; p.k = a->k; p.batch = a->batch;
+    p.lda = a->stride_a; p.ldb = a->stride_b; p.ldc = a->stride_c;
+    p.a_batch = a->stride_a_batch; p.b_batch = a->stride_b_batch; p.c_batch = a->stride_c_batch;
+    if (a->scale_mode == B200_SCALE_MX) {
+        p.sfa_stride = (a->m + 127) / 128;
+        p.sfb_stride = (a->n + 127) / 128;
+    } else {
+        p.sfa_stride = a->stride_sfa;
+        p.sfb_stride = a->stride_sfb;
+    }
+    p.sfa_batch = a->stride_sfa_batch; p.sfb_batch = a->stride_sfb_batch;
+    p.scale_mode = a->scale_mode; p.b_layout = a->b_layout; p.out_dtype = a->out_dtype;
+    dim3 grid(static_cast<unsigned>((a->n + 127) / 128), static_cast<unsigned>(a->m), static_cast<unsigned>(a->batch));
+    gemm_simple_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+
+int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
+    Plan pl;
+    if (!h) return B200_ERR_BAD_ARG;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const size_t esz = h->out_dtype == B200_OUT_BF16 ? 2 : 4;
+    const size_t a_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_a_batch * h->batch : h->stride_a * h->m);
+    const size_t b_bytes = static_cast<size_t>(h->b_layout == B200_B_FLAT_16x16
+                                                   ? (h->batch > 1 ? h->stride_b_batch * h->batch : h->n * h->k)
+                                                   : (h->batch > 1 ? h->stride_b_batch * h->batch : h->stride_b * h->n));
+    const size_t c_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_c_batch * h->batch : h->stride_c * h->m) * esz;
+    size_t sfa_bytes = 0, sfb_bytes = 0;
+    if (h->scale_mode == B200_SCALE_BLOCK) {
+        sfa_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_sfa_batch * h->batch : h->stride_sfa * (h->k / 128)) * 4;
+        sfb_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_sfb_batch * h->batch : h->stride_sfb * (h->n / 128)) * 4;
+    } else if (h->scale_mode == B200_SCALE_MX) {
+        sfa_bytes = h->batch > 1 ? static_cast<size_t>(h->stride_sfa_batch * h->batch) : b200_mx_sf_bytes(h->m, h->k);
+        sfb_bytes = h->batch > 1 ? static_cast<size_t>(h->stride_sfb_batch * h->batch) : b200_mx_sf_bytes(h->n, h->k);
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if ((rc = ensure(ds, 0, a_bytes)) || (rc = ensure(ds, 1, b_bytes)) || (rc = ensure(ds, 2, c_bytes)) ||
+            (rc = ensure(ds, 3, sfa_bytes + 16)) || (rc = ensure(ds, 4, sfb_bytes + 16)) || (rc = ensure(ds, 5, 64)))
+            return rc;
+    }
+    b200_gemm_args d = *h;
+    d.ptr_a = ds->buf[0];
+    d.ptr_b = ds->buf[1];
+    d.ptr_c = ds->buf[2];
+    rc = validate(&d, ds->sm_count, &pl);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(ds->buf[0], h->ptr_a, a_bytes, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(ds->buf[1], h->ptr_b, b_bytes, cudaMemcpyHostToDevice, st));
+    if (sfa_bytes) {
+        CU_TRY(cudaMemcpyAsync(ds->buf[3], h->ptr_sfa, sfa_bytes, cudaMemcpyHostToDevice, st));
+        CU_TRY(cudaMemcpyAsync(ds->buf[4], h->ptr_sfb, sfb_bytes, cudaMemcpyHostToDevice, st));
+        d.ptr_sfa = ds->buf[3];
+        d.ptr_sfb = ds->buf[4];
+    }
+    if (h->scale_mode == B200_SCALE_TENSOR) {
+        float* sc = static_cast<float*>(ds->buf[5]);
+        if (h->ptr_scale_a) {
+            CU_TRY(cudaMemcpyAsync(sc, h->ptr_scale_a, 4, cudaMemcpyHostToDevice, st));
+            d.ptr_scale_a = sc;
+        }
+        if (h->ptr_scale_b) {
+            CU_TRY(cudaMemcpyAsync(sc + 1, h->ptr_scale_b, 4, cudaMemcpyHostToDevice, st));
+            d.ptr_scale_b = sc + 1;
+        }
+    }
+    rc = b200_gemm_a8w8(&d, st);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(h->ptr_c, ds->buf[2], c_bytes, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return B200_OK;
+}
+
+// ---- layout ----------------------------------------------------------------------------------------
+static int shuffle_common(const void* src, void* dst, int64_t n, int64_t k, int32_t kn, bool to_flat, void* stream) {
+    if (!src || !dst || n <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (n % 16 != 0 || k % 16 != 0) return B200_ERR_UNSUPPORTED;
+    if (!aligned16(src) || !aligned16(dst)) return B200_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kn) {
+        dim3 grid(static_cast<unsigned>((n + 255) / 256), static_cast<unsigned>((k + 63) / 64));
+        if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+        if (to_flat) shuffle_kn_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), n, k);
+        else shuffle_kn_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), n, k);
+    } else {
+        dim3 grid(static_cast<unsigned>((k / 16 + 15) / 16), static_cast<unsigned>(n / 16));
+        if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+        if (to_flat) shuffle_nk_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), n, k);
+        else shuffle_nk_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), n, k);
+    }
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_shuffle_b(const void* src, void* dst, int64_t n, int64_t k, int32_t src_is_kn, void* stream) {
+    return shuffle_common(src, dst, n, k, src_is_kn, true, stream);
+}
+int b200_unshuffle_b(const void* flat, void* dst, int64_t n, int64_t k, int32_t dst_is_kn, void* stream) {
+    return shuffle_common(flat, dst, n, k, dst_is_kn, false, stream);
+}
+
+// ---- quantisers ------------------------------------------------------------------------------------
+static unsigned grid_for(int64_t work_items, int threads) {
+    int64_t blocks = (work_items + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    return static_cast<unsigned>(blocks);
+}
+int b200_cast_e4m3(const float* x, void* q, int64_t count, void* stream) {
+    if (!x || !q || count <= 0) return B200_ERR_BAD_ARG;
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3)) return B200_ERR_UNSUPPORTED;
+    cast_e4m3_kernel<<<grid_for(count / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<uint8_t*>(q), count);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+size_t b200_quantize_tensor_workspace(void) { return 256; }
+int b200_quantize_tensor(const float* x, void* q, float* scale, int64_t count, void* workspace, void* stream) {
+    if (!x || !q || !scale || !workspace || count <= 0) return B200_ERR_BAD_ARG;
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(workspace) & 3)) return B200_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int* amax = static_cast<unsigned int*>(workspace);
+    CU_TRY(cudaMemsetAsync(amax, 0, sizeof(unsigned int), st));
+    amax_kernel<<<grid_for(count / 4 + 1, 256), 256, 0, st>>>(x, count, amax);
+    CU_TRY(cudaGetLastError());
+    quant_tensor_kernel<<<grid_for(count / 4 + 1, 256), 256, 0, st>>>(x, static_cast<uint8_t*>(q), scale, count, amax);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(2);
+    return B200_OK;
+}
+int b200_quantize_1x128(const float* x, void* q, float* sfa, int64_t m, int64_t k, void* stream) {
+    if (!x || !q || !sfa || m <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (k % 128 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3)) return B200_ERR_UNSUPPORTED;
+    const int64_t warps = m * (k / 128);
+    const int64_t blocks = (warps + 7) / 8;
+    if (blocks > 0x7FFFFFFF) return B200_ERR_TOO_LARGE;
+    quant_1x128_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<uint8_t*>(q), sfa, m, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_quantize_128x128(const float* x, void* q, float* sfb, int64_t n, int64_t k, void* stream) {
+    if (!x || !q || !sfb || n <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (n % 128 != 0 || k % 128 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3)) return B200_ERR_UNSUPPORTED;
+    dim3 grid(static_cast<unsigned>(k / 128), static_cast<unsigned>(n / 128));
+    if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+    quant_128x128_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<uint8_t*>(q), sfb, n, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_quantize_mx32(const float* x, void* q, void* sf, int64_t rows, int64_t k, void* stream) {
+    if (!x || !q || !sf || rows <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (k % 32 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3)) return B200_ERR_UNSUPPORTED;
+    const int64_t threads = rows * (k / 32) * 8;
+    const int64_t blocks = (threads + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return B200_ERR_TOO_LARGE;
+    quant_mx32_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+size_t b200_mx_sf_bytes(int64_t rows, int64_t k) {
+    if (rows <= 0 || k <= 0) return 0;
+    return static_cast<size_t>((k + 127) / 128) * static_cast<size_t>((rows + 127) / 128) * 512;
+}
+int b200_mx_sf_relayout(const void* sf_logical, void* sf_atoms, int64_t rows, int64_t k, void* stream) {
+    if (!sf_logical || !sf_atoms || rows <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (k % 128 != 0 || (reinterpret_cast<uintptr_t>(sf_logical) & 3) || !aligned16(sf_atoms)) return B200_ERR_UNSUPPORTED;
+    const int64_t words = (k / 128) * ((rows + 127) / 128) * 128;
+    const int64_t blocks = (words + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return B200_ERR_TOO_LARGE;
+    mx_sf_relayout_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(sf_logical), static_cast<uint32_t*>(sf_atoms), rows, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+
+// ---- seeded inputs ---------------------------------------------------------------------------------
+void b200_fill_uniform(float* out, size_t count, uint64_t seed, uint32_t tensor_id, float lo, float hi) {
+    const uint64_t key = stream_key(seed, tensor_id);
+    const float span = hi - lo;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < static_cast<long long>(count); ++i) {
+        const uint32_t r = static_cast<uint32_t>(draw64(key, static_cast<uint64_t>(i)) >> 40);
+        const float u = static_cast<float>(r) * (1.0f / 16777216.0f);
+        volatile float prod = span * u;      // keep the multiply and the add separately rounded
+        out[i] = lo + prod;
+    }
+}
+void b200_fill_normal(float* out, size_t count, uint64_t seed, uint32_t tensor_id) {
+    const uint64_t key = stream_key(seed, tensor_id);
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < static_cast<long long>(count); ++i) {
+        const uint64_t d = draw64(key, static_cast<uint64_t>(i));
+        const uint32_t r1 = static_cast<uint32_t>(d >> 40);
+        const uint32_t r2 = static_cast<uint32_t>(d >> 8) & 0xFFFFFFu;
+        const double u1 = (static_cast<double>(r1) + 1.0) * (1.0 / 16777216.0);
+        const double u2 = static_cast<double>(r2) * (1.0 / 16777216.0);
+        out[i] = static_cast<float>(std::sqrt(-2.0 * std::log(u1)) * std::cos(6.283185307179586 * u2));
+    }
+}
+
+// ---- status ------------------------------------------------------------------------------------------
+int b200_last_status(void) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    CU_TRY(cudaDeviceSynchronize());
+    int v = 0;
+    CU_TRY(cudaMemcpy(&v, ds->status_ptr, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) CU_TRY(cudaMemset(ds->status_ptr, 0, sizeof(int)));
+    return v;
+}
+int b200_last_cuda_error(void) { return g_last_cuda; }
+const char* b200_strerror(int code) {
+    switch (code) {
+        case B200_OK: return "ok";
+        case B200_ERR_BAD_ARG: return "bad argument";
+        case B200_ERR_UNSUPPORTED: return "unsupported shape, stride or alignment";
+        case B200_ERR_CUDA: return "CUDA call failed";
+        case B200_ERR_DEVICE_TIMEOUT: return "bounded device wait expired";
+        case B200_ERR_NO_DEVICE: return "no sm_100 device";
+        case B200_ERR_TOO_LARGE: return "request exceeds an internal capacity";
+        default: return "unknown";
+    }
+}
+int b200_sm_count(void) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    return rc ? rc : ds->sm_count;
+}
+int b200_release(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[dev];
+    for (int i = 0; i < 8; ++i) {
+        if (s.buf[i]) cudaFree(s.buf[i]);
+        s.buf[i] = nullptr;
+        s.cap[i] = 0;
+    }
+    if (g_scratch[dev].ptr) cudaFree(g_scratch[dev].ptr);
+    g_scratch[dev].ptr = nullptr;
+    g_scratch[dev].cap = 0;
+    return B200_OK;
+}
+const char* b200_version(void) { return "b200gemm 0.1 (sm_100a)"; }
+uint64_t b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,140 @@
+/*
+ * b200gemm -- C ABI of the sm_100a A8W8 FP8 (OCP E4M3) GEMM library (libb200gemm.so).
+ *
+ * The reference (carlushuang/gcnasm) has no plugin or FFI layer: each example's main() fills a
+ * POD `kargs` struct and launches `kernel<Traits><<<grid, block>>>(kargs)` on the default
+ * stream.  The entry points below sit exactly at that seam; each comment names the reference
+ * launch site or host function it replaces.  All pointers are plain device (or, where stated,
+ * host) addresses; no C++ or framework types cross this boundary.  Every function returns 0 on
+ * success or a negative B200_ERR_* code; nothing here falls back to the CPU.
+ */
+#ifndef B200GEMM_H
+#define B200GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums ----------------------------------------------------------------------------- */
+enum b200_scale_mode {
+    B200_SCALE_NONE   = 0, /* C = A.B^T, the reference's gemm_a8w8_8wave / flatmm_a8w8 semantics        */
+    B200_SCALE_TENSOR = 1, /* C = (A.B^T) * scale_a * scale_b, one fp32 per tensor (device scalars)      */
+    B200_SCALE_BLOCK  = 2, /* A: 1x128 groups, SFA fp32 [K/128][M]; B: 128x128 blocks, SFB [N/128][K/128] */
+    B200_SCALE_MX     = 3  /* MXFP8: one E8M0 byte per 1x32 block of A and of B (see b200_mx_sf_relayout) */
+};
+enum b200_b_layout {
+    B200_B_NK_ROWMAJOR = 0, /* B[N][K], K contiguous (gemm_a8w8_8wave.cc, block_scale_gemm)              */
+    B200_B_FLAT_16x16  = 1  /* shuffle_b output [N/16][K/16][16][16] (opus_fmm/flatmm_a8w8_gfx950.cc)     */
+};
+enum b200_out_dtype { B200_OUT_F32 = 0, B200_OUT_BF16 = 1 };
+enum b200_tile_hint {
+    B200_TILE_AUTO = 0, B200_TILE_128x128 = 1, B200_TILE_128x256 = 2, B200_TILE_DECODE = 3,
+    B200_TILE_PAIR_256x256 = 4, B200_TILE_128x64 = 5, B200_TILE_PAIR_256x128 = 6
+};
+enum b200_error {
+    B200_OK = 0,
+    B200_ERR_BAD_ARG = -1,       /* null pointer, non-positive size, unknown enum                         */
+    B200_ERR_UNSUPPORTED = -2,   /* shape/stride/alignment the kernels do not cover (see b200_gemm_check)  */
+    B200_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; b200_last_cuda_error() has the code */
+    B200_ERR_DEVICE_TIMEOUT = -4,/* a bounded device-side wait expired (b200_last_status)                  */
+    B200_ERR_NO_DEVICE = -5,     /* no sm_100 device / driver entry point unavailable                      */
+    B200_ERR_TOO_LARGE = -6      /* request exceeds a fixed internal capacity                              */
+};
+
+/* ---- GEMM arguments ---------------------------------------------------------------------- */
+/* Superset of the three reference kargs structs, with 64-bit strides:
+ *   opus_gemm_kargs            opus_gemm/gemm_a8w8_8wave.cc:99-113
+ *   opus_gemm_kargs (+scales)  opus_gemm/block_scale_gemm/gemm_a8w8_blockscale_common.h:4-25
+ *   opus_fmm_kargs             opus_fmm/flatmm_a8w8_gfx950.cc:107-122 (ptr_bias is unused there and dropped)
+ * Strides are in ELEMENTS, as in the reference.  A is [batch][M][K] e4m3, B is [batch][N][K] e4m3
+ * (or its flat image), C is [batch][M][N] fp32 or bf16.                                                 */
+typedef struct b200_gemm_args {
+    const void* ptr_a;
+    const void* ptr_b;
+    void*       ptr_c;
+    int64_t m, n, k, batch;
+    int64_t stride_a, stride_b, stride_c;                    /* row strides; stride_b ignored for flat B   */
+    int64_t stride_a_batch, stride_b_batch, stride_c_batch;
+    const void* ptr_sfa;          /* BLOCK: fp32 [K/128][M] (M contiguous).  MX: relayouted E8M0 bytes     */
+    const void* ptr_sfb;          /* BLOCK: fp32 [N/128][K/128].             MX: relayouted E8M0 bytes     */
+    int64_t stride_sfa;           /* BLOCK: elements between K groups of SFA (= M in the reference)        */
+    int64_t stride_sfb;           /* BLOCK: elements between N blocks of SFB (= K/128 in the reference)    */
+    int64_t stride_sfa_batch, stride_sfb_batch;
+    const float* ptr_scale_a;     /* TENSOR: device fp32 scalars; null means 1.0                           */
+    const float* ptr_scale_b;
+    int32_t scale_mode;           /* b200_scale_mode  */
+    int32_t b_layout;             /* b200_b_layout    */
+    int32_t out_dtype;            /* b200_out_dtype   */
+    int32_t tile_hint;            /* b200_tile_hint   */
+} b200_gemm_args;
+
+/* Replaces the launches `gemm_a8w8_kernel<Traits><<<grid,block>>>(kargs)` (gemm_a8w8_8wave.cc:738),
+ * `gemm_a8w8_blockscale_kernel<GemmTraits><<<grid,block>>>(kargs)` (gemm_a8w8_blockscale_host.cc:257)
+ * and `flatmm_kernel<Traits><<<grid,block>>>(kargs)` (flatmm_a8w8_gfx950.cc:780).  Asynchronous on
+ * `cuda_stream` (a cudaStream_t, 0 = default stream); buffers are caller-owned device memory.           */
+int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream);
+
+/* Validates `args` exactly as b200_gemm_a8w8 would, without touching the GPU. Also reports the tile
+ * configuration the launcher would pick (a b200_tile_hint value) when `chosen_tile` is not null.        */
+int b200_gemm_check(const b200_gemm_args* args, int32_t* chosen_tile);
+
+/* Same contract as b200_gemm_a8w8 but computed by a one-thread-per-output CUDA kernel that mirrors the
+ * host gemm_ref loops (gemm_a8w8_8wave.cc:601-612, gemm_a8w8_blockscale_host.cc:66-90): the device-side
+ * checker for problem sizes the CPU loops cannot finish.  MX scales are read in the relayouted form.     */
+int b200_gemm_a8w8_simple(const b200_gemm_args* args, void* cuda_stream);
+
+/* Whole reference main() data path with HOST buffers (hipMemcpy H2D -> launch -> hipMemcpy D2H,
+ * gemm_a8w8_blockscale_host.cc:212-226,257,262): copies the operands in `args` (host pointers) to
+ * device buffers owned by the library, runs the GEMM and copies C back; returns after the copy-back.
+ * Device buffers are cached per device and grown on demand; b200_release() frees them.                  */
+int b200_gemm_a8w8_host(const b200_gemm_args* host_args, void* cuda_stream);
+
+/* ---- weight pre-shuffle -------------------------------------------------------------------- */
+/* shuffle_b (flatmm_a8w8_gfx950.cc:638-681) on the device: src is [K][N] row-major when src_is_kn != 0
+ * (the reference's input) or [N][K] row-major otherwise; dst is [N/16][K/16][16][16].  Bit-exact byte
+ * permutation; N % 16 == 0 and K % 16 == 0 required (asserts at :650-651).                              */
+int b200_shuffle_b(const void* src, void* dst, int64_t n, int64_t k, int32_t src_is_kn, void* cuda_stream);
+/* inverse: flat -> [K][N] (dst_is_kn != 0) or [N][K] */
+int b200_unshuffle_b(const void* flat, void* dst, int64_t n, int64_t k, int32_t dst_is_kn, void* cuda_stream);
+
+/* ---- quantisers (device) -------------------------------------------------------------------- */
+/* The reference has no quantiser (operands are static_cast<fp8>(uniform float),
+ * gemm_a8w8_blockscale_host.cc:32-44); these implement the benchmark configurations' rules:
+ * scale = amax/448 (1.0 for an all-zero group), q = e4m3_rne_satfinite(x / scale).                      */
+int b200_cast_e4m3(const float* x, void* q, int64_t count, void* cuda_stream);
+/* workspace: at least b200_quantize_tensor_workspace() bytes of device scratch */
+int b200_quantize_tensor(const float* x, void* q, float* scale, int64_t count, void* workspace, void* cuda_stream);
+size_t b200_quantize_tensor_workspace(void);
+int b200_quantize_1x128(const float* x, void* q, float* sfa, int64_t m, int64_t k, void* cuda_stream);   /* sfa [K/128][M] */
+int b200_quantize_128x128(const float* x, void* q, float* sfb, int64_t n, int64_t k, void* cuda_stream); /* sfb [N/128][K/128] */
+/* MX 1x32: e = floor(log2(amax)) - 8, byte = clamp(e + 127, 0, 254), q = e4m3(x * 2^-e); sf is [rows][K/32] */
+int b200_quantize_mx32(const float* x, void* q, void* sf, int64_t rows, int64_t k, void* cuda_stream);
+/* Re-lays logical E8M0 scales [rows][K/32] into the tensor-core atom order the MX GEMM reads:
+ * [K/128][ceil(rows/128)][32][4][4] bytes, padded rows = 127 (scale 1.0).  Size: b200_mx_sf_bytes().     */
+int b200_mx_sf_relayout(const void* sf_logical, void* sf_atoms, int64_t rows, int64_t k, void* cuda_stream);
+size_t b200_mx_sf_bytes(int64_t rows, int64_t k);
+
+/* ---- seeded inputs (host) --------------------------------------------------------------------- */
+/* The reference draws inputs from std::random_device (gemm_a8w8_8wave.cc:570-571), which cannot be
+ * reproduced; these counter-based generators replace it.  Element i depends only on (seed, tensor_id, i). */
+void b200_fill_uniform(float* host_out, size_t count, uint64_t seed, uint32_t tensor_id, float lo, float hi);
+void b200_fill_normal(float* host_out, size_t count, uint64_t seed, uint32_t tensor_id);
+
+/* ---- status / housekeeping --------------------------------------------------------------------- */
+/* Device status word of the current device: 0, or the code of the first bounded wait that expired
+ * since the last call (which also clears it).  Synchronises the device.                                  */
+int b200_last_status(void);
+int b200_last_cuda_error(void);
+const char* b200_strerror(int code);
+int b200_sm_count(void);
+int b200_release(void);              /* frees cached device buffers of b200_gemm_a8w8_host              */
+const char* b200_version(void);
+uint64_t b200_launch_count(void);    /* kernels launched by this library in this process                  */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GEMM_H */
