@@ -69,7 +69,7 @@ def build_drivers(force: bool = False) -> list:
         deps = [src, LIB] + [os.path.join(DRIVERS, h) for h in os.listdir(DRIVERS) if h.endswith(".h")]
         if force or _newer(exe, deps):
             subprocess.check_call([
-                _nvcc(), "-O3", "-std=c++17", "-ccbin", _host_cxx(), "-Xcompiler", "-fopenmp,-fno-fast-math",
+                _nvcc(), "-O3", "-std=c++17", "-Wno-deprecated-gpu-targets", "-ccbin", _host_cxx(), "-Xcompiler", "-fopenmp,-fno-fast-math",
                 "-I", os.path.join(ROOT, "include"), "-o", exe, src,
                 "-L", PKG, "-lb200gemm", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/..",
             ])

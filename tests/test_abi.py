@@ -1,0 +1,147 @@
+"""CPU: the C-ABI surface -- the library loads, exports every symbol the header declares, the Python
+struct mirrors the C struct, argument validation returns the documented codes, and nothing computes
+without a GPU."""
+import ctypes as C
+import os
+import re
+import subprocess
+import tempfile
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+HEADER = os.path.join(ROOT, "include", "b200gemm.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(native):
+    from gcnasm_b200 import _lib
+
+    declared = _declared_symbols()
+    assert len(declared) >= 20
+    for name in declared:
+        assert hasattr(native, name), f"{name} declared in include/b200gemm.h but not exported"
+    assert sorted(_lib.EXPORTS) == declared
+
+
+def test_struct_layout_matches_c(native):
+    from gcnasm_b200._lib import GemmArgs
+
+    fields = [f[0] for f in GemmArgs._fields_]
+    prog = '#include <stdio.h>\n#include <stddef.h>\n#include "b200gemm.h"\nint main(){printf("%zu", sizeof(b200_gemm_args));' + "".join(
+        f'printf(" %zu", offsetof(b200_gemm_args, {f}));' for f in fields) + "return 0;}"
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "t.c")
+        open(src, "w").write(prog)
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), src, "-o", os.path.join(d, "t")])
+        out = subprocess.check_output([os.path.join(d, "t")]).decode().split()
+    assert int(out[0]) == C.sizeof(GemmArgs)
+    for f, off in zip(fields, out[1:]):
+        assert getattr(GemmArgs, f).offset == int(off), f
+
+
+def _args(**kw):
+    from gcnasm_b200._lib import GemmArgs
+
+    a = GemmArgs()
+    a.ptr_a, a.ptr_b, a.ptr_c = 0x1000, 0x2000, 0x3000
+    a.m, a.n, a.k, a.batch = 256, 512, 1024, 1
+    a.stride_a, a.stride_b, a.stride_c = 1024, 1024, 512
+    a.stride_a_batch, a.stride_b_batch, a.stride_c_batch = 256 * 1024, 512 * 1024, 256 * 512
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+def test_validation_codes(native):
+    from gcnasm_b200 import _lib as L
+
+    tile = C.c_int32(0)
+    chk = lambda a: native.b200_gemm_check(C.byref(a), C.byref(tile))
+    assert chk(_args()) == L.OK and tile.value in (L.TILE_128x128, L.TILE_128x256)
+    assert native.b200_gemm_check(None, None) == L.ERR_BAD_ARG
+    assert chk(_args(ptr_a=0)) == L.ERR_BAD_ARG
+    # non-positive sizes are rejected like the reference's "Invalid problem size" (gemm_a8w8_8wave.cc:685-688)
+    for f in ("m", "n", "k", "batch"):
+        assert chk(_args(**{f: 0})) == L.ERR_BAD_ARG
+        assert chk(_args(**{f: -4})) == L.ERR_BAD_ARG
+    assert chk(_args(scale_mode=9)) == L.ERR_BAD_ARG
+    assert chk(_args(stride_a=1000)) == L.ERR_BAD_ARG            # row pitch smaller than K
+    assert chk(_args(k=1000, stride_a=1000, stride_b=1000)) == L.ERR_UNSUPPORTED   # K % 16 != 0
+    assert chk(_args(ptr_a=0x1004)) == L.ERR_UNSUPPORTED          # TMA base alignment
+    # block scale: N % 128 and K % 128 as gemm_a8w8_blockscale_host.cc:183, M arbitrary
+    bs = dict(scale_mode=L.SCALE_BLOCK, ptr_sfa=0x4000, ptr_sfb=0x5000, stride_sfa=256, stride_sfb=8)
+    assert chk(_args(**bs)) == L.OK
+    assert chk(_args(**{**bs, "m": 77, "stride_sfa": 77})) == L.OK
+    assert chk(_args(**{**bs, "n": 500, "stride_c": 500})) == L.ERR_UNSUPPORTED
+    assert chk(_args(**{**bs, "k": 1040, "stride_a": 1040, "stride_b": 1040, "stride_sfb": 9})) == L.ERR_UNSUPPORTED
+    assert chk(_args(**{**bs, "ptr_sfa": 0})) == L.ERR_BAD_ARG
+    # flat B: whole 16x16 blocks (asserts at flatmm_a8w8_gfx950.cc:650-651)
+    assert chk(_args(b_layout=L.B_FLAT_16x16)) == L.OK
+    assert chk(_args(b_layout=L.B_FLAT_16x16, n=500, stride_c=500)) == L.ERR_UNSUPPORTED
+    # tile selection: skinny M goes to the decode kernel, MX to 128x128
+    assert chk(_args(m=16)) == L.OK and tile.value == L.TILE_DECODE
+    assert chk(_args(**{**bs, "m": 64, "stride_sfa": 64})) == L.OK and tile.value == L.TILE_DECODE
+    assert chk(_args(m=65)) == L.OK and tile.value != L.TILE_DECODE
+    assert chk(_args(m=4096, n=7168, k=2048, stride_a=2048, stride_b=2048, stride_c=7168)) == L.OK and tile.value == L.TILE_128x256
+    assert chk(_args(m=128, tile_hint=L.TILE_DECODE)) == L.ERR_UNSUPPORTED
+    mx = dict(scale_mode=L.SCALE_MX, ptr_sfa=0x4000, ptr_sfb=0x5000)
+    assert chk(_args(**mx)) == L.OK and tile.value == L.TILE_128x128
+    assert chk(_args(**mx, k=1056, stride_a=1056, stride_b=1056)) == L.ERR_UNSUPPORTED
+
+
+def test_helpers_and_strings(native):
+    assert native.b200_strerror(0) == b"ok"
+    assert b"unsupported" in native.b200_strerror(-2)
+    assert native.b200_version().startswith(b"b200gemm")
+    assert native.b200_mx_sf_bytes(8192, 8192) == 64 * 64 * 512
+    assert native.b200_mx_sf_bytes(129, 128) == 2 * 512
+    assert native.b200_quantize_tensor_workspace() >= 4
+    assert native.b200_launch_count() >= 0
+
+
+def test_layout_and_quantiser_argument_checks(native):
+    from gcnasm_b200 import _lib as L
+
+    assert native.b200_shuffle_b(0x1000, 0x2000, 24, 16, 1, None) == L.ERR_UNSUPPORTED
+    assert native.b200_shuffle_b(0x1000, 0x2000, 16, 24, 1, None) == L.ERR_UNSUPPORTED
+    assert native.b200_shuffle_b(None, 0x2000, 16, 16, 1, None) == L.ERR_BAD_ARG
+    assert native.b200_quantize_1x128(0x1000, 0x2000, 0x3000, 4, 100, None) == L.ERR_UNSUPPORTED
+    assert native.b200_quantize_128x128(0x1000, 0x2000, 0x3000, 100, 128, None) == L.ERR_UNSUPPORTED
+    assert native.b200_quantize_mx32(0x1000, 0x2000, 0x3000, 4, 48, None) == L.ERR_UNSUPPORTED
+    assert native.b200_mx_sf_relayout(0x1000, 0x2000, 4, 96, None) == L.ERR_UNSUPPORTED
+
+
+def test_host_generators_match_oracle(native, O):
+    from gcnasm_b200 import api
+
+    for seed, tid in ((1234, 0), (7, 9)):
+        assert np.array_equal(api.fill_uniform(10007, seed, tid, -1.0, 1.0), O.fill_uniform(10007, seed, tid, -1.0, 1.0))
+        assert np.array_equal(api.fill_normal(10007, seed, tid), O.fill_normal(10007, seed, tid))
+
+
+def test_no_gpu_means_error_not_fallback(native):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("this check is for GPU-less machines")
+    from gcnasm_b200 import _lib as L
+
+    assert native.b200_gemm_a8w8(C.byref(_args()), None) in (L.ERR_NO_DEVICE, L.ERR_CUDA)
+    assert native.b200_sm_count() < 0
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from gcnasm_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libb200gemm.so")
+    with pytest.raises(ImportError):
+        _lib.lib()

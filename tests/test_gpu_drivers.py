@@ -1,0 +1,61 @@
+"""GPU: the three C++ host drivers keep the reference's command line and self-check."""
+import os
+import re
+import subprocess
+
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+BIN = os.path.join(ROOT, "gcnasm_b200", "bin")
+
+
+@pytest.fixture(scope="module")
+def drivers(native):
+    from gcnasm_b200 import build
+
+    build.build_drivers()
+    return BIN
+
+
+def run(drivers, name, *args):
+    out = subprocess.run([os.path.join(drivers, name), *args, "--warmup", "5", "--iters", "10"], capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    return out.stdout
+
+
+def test_gemm_a8w8_8wave_default_and_flags(drivers):
+    out = run(drivers, "gemm_a8w8_8wave")                               # reference defaults: 256x512x256, batch 8
+    assert "Launching GEMM kernel: M=256, N=512, K=256" in out
+    assert out.count("VALID") >= 9 and "ALL BATCHES VALID" in out and "FAIL" not in out
+    assert re.search(r"Kernel Performance: avg_time=\d+\.\d+ ms, \d+\.\d+ TFlops", out)
+    out = run(drivers, "gemm_a8w8_8wave", "-m", "256", "-n", "512", "-k", "1024", "-b", "1", "--scale", "tensor", "--out", "bf16")
+    assert "ALL BATCHES VALID" in out
+
+
+def test_gemm_a8w8_8wave_rejects_bad_size(drivers):
+    out = subprocess.run([os.path.join(drivers, "gemm_a8w8_8wave"), "-m", "0"], capture_output=True, text=True)
+    assert out.returncode == 1 and "Invalid problem size" in out.stderr
+
+
+def test_blockscale_driver(drivers):
+    out = run(drivers, "gemm_a8w8_blockscale", "-m=512", "-n=768", "-k=1024", "-b=2", "-v=1")
+    assert "Validating GPU results against CPU reference" in out and "ALL BATCHES VALID" in out
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "512", "-n", "768", "-k", "1024", "-b", "1", "-v", "1", "--dist", "n01", "--out", "bf16")
+    assert "ALL BATCHES VALID" in out
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "256", "-n", "384", "-k", "512", "-b", "1", "-v", "1", "--scale", "mx")
+    assert "ALL BATCHES VALID" in out
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "256", "-n", "384", "-k", "512", "-b", "1")       # -v defaults to 0
+    assert "VALID" not in out and "Kernel Performance" in out
+    bad = subprocess.run([os.path.join(drivers, "gemm_a8w8_blockscale"), "-n", "500"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "multiples of GROUP_M/GROUP_N/GROUP_K" in bad.stderr
+
+
+def test_flatmm_driver(drivers):
+    out = run(drivers, "flatmm_a8w8")
+    assert "Shuffling B matrix for FlatMM layout (batch=8)" in out and "BIT-EXACT" in out
+    assert "Launching FlatMM kernel: M=256, N=512, K=256" in out and "ALL BATCHES VALID" in out
+    out = run(drivers, "flatmm_a8w8", "-m", "16", "-n", "2304", "-k", "1024", "-b", "1", "--scale", "block", "--out", "bf16")
+    assert "ALL BATCHES VALID" in out and "tile_config=3" in out

@@ -1,0 +1,107 @@
+"""GPU: the BASELINE configurations at full size.  The CPU oracle cannot finish these in seconds, so they are
+checked (a) on sampled rows against the oracle, (b) on row slabs against the one-thread-per-output device
+kernel (itself bit-identical to the oracle on small shapes), and (c) through size-independent properties:
+run-to-run determinism, exact power-of-two scale linearity and shard/slice consistency."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+from test_gpu_gemm import DEV, T, status_ok
+
+pytestmark = pytest.mark.gpu
+
+
+def _rows(m, count, seed):
+    rng = np.random.default_rng(seed)
+    return np.sort(rng.choice(m, count, replace=False))
+
+
+@pytest.fixture(scope="module")
+def config2(api, O):
+    m, n, k = 4096, 7168, 2048
+    xa = torch.from_numpy(api.fill_normal((m, k), 1234, 0)).to(DEV)
+    xb = torch.from_numpy(api.fill_normal((n, k), 1234, 1)).to(DEV)
+    qa, sfa = api.quantize_1x128(xa)
+    qb, sfb = api.quantize_128x128(xb)
+    return m, n, k, qa, qb, sfa, sfb
+
+
+@pytest.mark.parametrize("tile", [1, 2])
+def test_config2_blockscale_full(api, O, config2, tile):
+    m, n, k, qa, qb, sfa, sfb = config2
+    c = api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out_dtype=torch.bfloat16, tile=tile)
+    status_ok(api)
+    # (a) sampled rows on the CPU oracle
+    rows = _rows(m, 6, 2)
+    ha, hb = qa.cpu().numpy(), qb.cpu().numpy()
+    hsa, hsb = sfa.cpu().numpy(), sfb.cpu().numpy()
+    for r in rows:
+        ref = O.bf16_bits_to_f32(O.gemm_ref_blockscale(ha, hb, hsa, hsb, out_bf16=True, rows=(int(r), int(r) + 1)))
+        assert_close(O, c[r:r + 1].float().cpu().numpy(), ref, f"row {r}")
+    # (b) two 128-row slabs on the device checker
+    for r0 in (0, 3968):
+        ref = api.gemm_a8w8_blockscale(qa[r0:r0 + 128], qb, sfa[:, r0:r0 + 128].contiguous(), sfb,
+                                       out_dtype=torch.bfloat16, simple=True)
+        assert_close(O, c[r0:r0 + 128].float().cpu().numpy(), ref.float().cpu().numpy(), f"slab {r0}")
+    # (c) determinism and N-shard consistency: computing a column shard alone gives the same bits
+    c2 = api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out_dtype=torch.bfloat16, tile=tile)
+    assert torch.equal(c, c2)
+    shard = api.gemm_a8w8_blockscale(qa, qb[1792:3584], sfa, sfb[14:28].contiguous(), out_dtype=torch.bfloat16, tile=tile)
+    assert torch.equal(shard, c[:, 1792:3584])
+
+
+def test_config3_mxfp8_full(api, O):
+    m = n = k = 8192
+    xa = torch.from_numpy(api.fill_normal((m, k), 1234, 0)).to(DEV)
+    xb = torch.from_numpy(api.fill_normal((n, k), 1234, 1)).to(DEV)
+    qa, ea, sa = api.quantize_mx32(xa)
+    qb, eb, sb = api.quantize_mx32(xb)
+    del xa, xb
+    c = api.gemm_a8w8_mx(qa, qb, sa, sb, out_dtype=torch.bfloat16)
+    status_ok(api)
+    hb, heb = qb.cpu().numpy(), eb.cpu().numpy()
+    for r in _rows(m, 3, 3):
+        ref = O.gemm_ref_mx(qa[r:r + 1].cpu().numpy(), hb, ea[r:r + 1].cpu().numpy(), heb)
+        assert_close(O, c[r:r + 1].float().cpu().numpy(), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref)), f"row {r}")
+    # a 128-row slab on the device checker (needs that slab's own scale atoms)
+    r0 = 4096
+    sa_slab = api.mx_sf_relayout(ea[r0:r0 + 128].contiguous(), 128, k)
+    ref = api.gemm_a8w8_mx(qa[r0:r0 + 128], qb, sa_slab, sb, out_dtype=torch.float32, simple=True)
+    assert_close(O, c[r0:r0 + 128].float().cpu().numpy(), ref.cpu().numpy(), "slab")
+    assert torch.equal(c, api.gemm_a8w8_mx(qa, qb, sa, sb, out_dtype=torch.bfloat16))
+
+
+def test_blockscale_8192_cube_sampled(api, O):
+    """the shape the throughput target is quoted on"""
+    m = n = k = 8192
+    xa = torch.from_numpy(api.fill_normal((m, k), 7, 0)).to(DEV)
+    xb = torch.from_numpy(api.fill_normal((n, k), 7, 1)).to(DEV)
+    qa, sfa = api.quantize_1x128(xa)
+    qb, sfb = api.quantize_128x128(xb)
+    del xa, xb
+    c = api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out_dtype=torch.bfloat16)
+    status_ok(api)
+    r0 = 8064
+    ref = api.gemm_a8w8_blockscale(qa[r0:r0 + 128], qb, sfa[:, r0:r0 + 128].contiguous(), sfb, out_dtype=torch.float32, simple=True)
+    assert_close(O, c[r0:r0 + 128].float().cpu().numpy(), ref.cpu().numpy(), "slab")
+    ha, hb, hsa, hsb = qa.cpu().numpy(), qb.cpu().numpy(), sfa.cpu().numpy(), sfb.cpu().numpy()
+    for r in _rows(m, 2, 5):
+        ref = O.bf16_bits_to_f32(O.gemm_ref_blockscale(ha, hb, hsa, hsb, out_bf16=True, rows=(int(r), int(r) + 1)))
+        assert_close(O, c[r:r + 1].float().cpu().numpy(), ref, f"row {r}")
+
+
+def test_scale_linearity_exact(api, O):
+    """power-of-two per-tensor scales only shift exponents: results scale exactly"""
+    m, n, k = 512, 1024, 1024
+    a = T(O.cast_e4m3(O.fill_uniform((m, k), 1, 0, 0.0, 1.0)))
+    b = T(O.cast_e4m3(O.fill_uniform((n, k), 1, 1, -0.5, 0.5)))
+    base = api.gemm_a8w8(a, b, out_dtype=torch.float32)
+    s2 = api.gemm_a8w8(a, b, torch.tensor([4.0], device=DEV), torch.tensor([0.125], device=DEV), out_dtype=torch.float32)
+    assert torch.equal(s2, base * 0.5)
+    # block scales all equal to 1 reproduce the unscaled product bit for bit
+    ones_a = torch.ones(k // 128, m, device=DEV)
+    ones_b = torch.ones(n // 128, k // 128, device=DEV)
+    bs = api.gemm_a8w8_blockscale(a, b, ones_a, ones_b, out_dtype=torch.float32)
+    assert_close(O, bs.cpu().numpy(), base.cpu().numpy(), "unit block scales")
+    status_ok(api)

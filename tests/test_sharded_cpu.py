@@ -1,0 +1,80 @@
+"""CPU, world_size 2 over gloo: the host logic of the N-sharded GEMM (partitioning, activation broadcast,
+optional all-gather).  The local GEMM is replaced by the oracle here -- this test covers the plumbing, the GPU
+tests cover the kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def test_shard_bounds():
+    from gcnasm_b200.sharded import shard_bounds
+
+    assert shard_bounds(57344, 8, 3) == (21504, 28672)
+    assert shard_bounds(7168, 1, 0) == (0, 7168)
+    assert [shard_bounds(1024, 4, r) for r in range(4)] == [(0, 256), (256, 512), (512, 768), (768, 1024)]
+    with pytest.raises(ValueError):
+        shard_bounds(1000, 2, 0)          # 500 is not a whole number of 128-column scale blocks
+    with pytest.raises(ValueError):
+        shard_bounds(1024, 3, 0)
+    with pytest.raises(ValueError):
+        shard_bounds(1024, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, tmp):
+    import sys
+
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from gcnasm_b200.sharded import ColumnShardedGemm, shard_bounds
+    from oracle import oracle as O
+
+    m, n, k = 48, 512, 256
+    a = O.cast_e4m3(O.fill_uniform((m, k), 3, 0, 0.0, 1.0))
+    b = O.cast_e4m3(O.fill_uniform((n, k), 3, 1, -0.5, 0.5))
+    sfa = O.fill_uniform((k // 128, m), 3, 2, 0.8, 1.2)
+    sfb = O.fill_uniform((n // 128, k // 128), 3, 3, 0.8, 1.2)
+    n0, n1 = shard_bounds(n, world, rank)
+
+    def cpu_gemm(ta, tb, tsfa, tsfb, out):
+        out.copy_(torch.from_numpy(O.gemm_ref_blockscale(ta.numpy(), tb.numpy(), tsfa.numpy(), tsfb.numpy())))
+
+    op = ColumnShardedGemm(torch.from_numpy(b[n0:n1].copy()), torch.from_numpy(sfb[n0 // 128:n1 // 128].copy()), n,
+                           gemm_fn=cpu_gemm, out_dtype=torch.float32)
+    # only the root holds the activation; the others pass zero-filled buffers
+    ta = torch.from_numpy(a.copy()) if rank == 0 else torch.zeros(m, k, dtype=torch.uint8)
+    tsfa = torch.from_numpy(sfa.copy()) if rank == 0 else torch.zeros(k // 128, m)
+    full = op(ta, tsfa, root=0, gather=True)
+    assert np.array_equal(ta.numpy(), a) and np.array_equal(tsfa.numpy(), sfa)      # broadcast arrived
+    ref = O.gemm_ref_blockscale(a, b, sfa, sfb)
+    got = torch.cat([full[r] for r in range(world)], dim=1).numpy()
+    ok = np.array_equal(got, ref)
+    shard = op(ta, tsfa, broadcast=False)
+    ok = ok and np.array_equal(shard.numpy(), ref[:, n0:n1])
+    open(os.path.join(tmp, f"ok{rank}"), "w").write("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_column_sharded_gemm_world2(tmp_path, O):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"ok{r}").read() == "1"
