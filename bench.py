@@ -118,9 +118,10 @@ def cpu_reference_arm(args, workload, rank, world):
     t0 = time.perf_counter()
     O.gemm_ref_blockscale(a, b, sfa, sfb, out_bf16=True)
     probe = time.perf_counter() - t0
-    # size a step to about 2 s of CPU work, bounded by the real M
-    rows = int(min(m, max(64, 64 * (2.0 / max(probe, 1e-3)))))
-    rows -= rows % 16
+    # size a step so that the whole run (warm-up + timed steps) stays near 90 s, at most 2 s per step
+    target = min(2.0, 90.0 / max(1, args.steps + args.warmup))
+    rows = int(min(m, max(16, 64 * (target / max(probe, 1e-3)))))
+    rows = max(16, rows - rows % 16)
     a = O.cast_e4m3(O.fill_normal((rows, k), SEED, 0))
     sfa = O.fill_uniform((k // 128, rows), SEED, 2, 0.8, 1.2)
     for _ in range(args.warmup):
