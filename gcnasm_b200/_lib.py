@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(_PKG, "libb200gemm.so")
 SCALE_NONE, SCALE_TENSOR, SCALE_BLOCK, SCALE_MX = 0, 1, 2, 3
 B_NK_ROWMAJOR, B_FLAT_16x16 = 0, 1
 OUT_F32, OUT_BF16 = 0, 1
-TILE_AUTO, TILE_128x128, TILE_128x256, TILE_DECODE, TILE_PAIR_256x256, TILE_128x64, TILE_PAIR_256x128 = range(7)
+(TILE_AUTO, TILE_128x128, TILE_128x256, TILE_DECODE, TILE_PAIR_256x256, TILE_128x64, TILE_PAIR_256x128,
+ TILE_PAIR_256x224, TILE_PAIR_256x192) = range(9)
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
 
 # every symbol include/b200gemm.h declares

@@ -14,6 +14,7 @@
 
 #include "aux_kernels.cuh"
 #include "decode_sm100.cuh"
+#include "gemm_pair_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace {
@@ -142,7 +143,7 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
     if (!a || !a->ptr_a || !a->ptr_b || !a->ptr_c) return B200_ERR_BAD_ARG;
     if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return B200_ERR_BAD_ARG;
     if (a->scale_mode < 0 || a->scale_mode > 3 || a->b_layout < 0 || a->b_layout > 1 || a->out_dtype < 0 ||
-        a->out_dtype > 1 || a->tile_hint < 0 || a->tile_hint > 6)
+        a->out_dtype > 1 || a->tile_hint < 0 || a->tile_hint > 8)
         return B200_ERR_BAD_ARG;
     if (a->m > 0x7FFFFFFF || a->n > 0x7FFFFFFF || a->k > 0x7FFFFFFF || a->batch > 65535) return B200_ERR_TOO_LARGE;
     if (a->stride_a < a->k || a->stride_c < a->n) return B200_ERR_BAD_ARG;
@@ -174,17 +175,47 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
     const bool decode_ok = a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
     int hint = a->tile_hint;
     if (hint == B200_TILE_DECODE && !decode_ok) return B200_ERR_UNSUPPORTED;
-    if (hint == B200_TILE_PAIR_256x256 || hint == B200_TILE_PAIR_256x128 || hint == B200_TILE_128x64)
-        return B200_ERR_UNSUPPORTED;
+    if (hint == B200_TILE_128x64) return B200_ERR_UNSUPPORTED;
+    const bool mx = a->scale_mode == B200_SCALE_MX;
+    // MX pair kernels address the scale atoms through a tensor map: batch strides in whole atoms
+    const bool mx_pair_ok = !mx || a->batch == 1 || (a->stride_sfa_batch % 512 == 0 && a->stride_sfb_batch % 512 == 0);
     if (hint == B200_TILE_AUTO) {
-        if (decode_ok) hint = B200_TILE_DECODE;
-        else if (a->scale_mode == B200_SCALE_MX) hint = B200_TILE_128x128;
-        else {
-            const int64_t t256 = ((a->m + 127) / 128) * ((a->n + 255) / 256) * a->batch;
-            hint = (t256 >= sm_count) ? B200_TILE_128x256 : B200_TILE_128x128;
+        if (decode_ok) {
+            hint = B200_TILE_DECODE;
+        } else {
+            // cost of a persistent schedule: rounds x time per tile (proportional to the tile's N)
+            const int pairs = sm_count / 2;
+            const int64_t tm2 = (a->m + 255) / 256, tm1 = (a->m + 127) / 128;
+            int64_t best = -1;
+            auto consider = [&](int tile, int bn, bool pair) {
+                const int64_t tiles = (pair ? tm2 : tm1) * ((a->n + bn - 1) / bn) * a->batch;
+                const int64_t units = pair ? pairs : sm_count;
+                const int64_t rounds = (tiles + units - 1) / units;
+                // weight = relative time per output column: pairs with wide tiles feed the tensor pipe best,
+                // narrow and single-CTA tiles re-read more of A/B per flop from L2
+                const int64_t w = pair ? (bn >= 192 ? 10 : 13) : (bn >= 256 ? 14 : 18);
+                const int64_t cost = rounds * bn * w;
+                if (best < 0 || cost < best) {
+                    best = cost;
+                    hint = tile;
+                }
+            };
+            if (mx) {
+                if (mx_pair_ok && a->m > 128) consider(B200_TILE_PAIR_256x256, 256, true);
+                consider(B200_TILE_128x128, 128, false);
+            } else {
+                if (a->m > 128) {
+                    consider(B200_TILE_PAIR_256x256, 256, true);
+                    consider(B200_TILE_PAIR_256x224, 224, true);
+                    consider(B200_TILE_PAIR_256x192, 192, true);
+                    consider(B200_TILE_PAIR_256x128, 128, true);
+                }
+                consider(B200_TILE_128x256, 256, false);
+                consider(B200_TILE_128x128, 128, false);
+            }
         }
     }
-    if (hint == B200_TILE_128x256 && a->scale_mode == B200_SCALE_MX) return B200_ERR_UNSUPPORTED;
+    if (mx && !(hint == B200_TILE_128x128 || (hint == B200_TILE_PAIR_256x256 && mx_pair_ok))) return B200_ERR_UNSUPPORTED;
     pl.tile = hint;
     if (hint == B200_TILE_DECODE) {
         pl.mt = a->m <= 16 ? 16 : (a->m <= 32 ? 32 : 64);
@@ -234,6 +265,62 @@ int launch_decode(const DecodeParams& p, int grid, cudaStream_t st) {
     CU_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
     return B200_OK;
+}
+
+// number of CTA pairs that can be resident at once (GPCs with an odd SM count strand one SM)
+template <class Kernel>
+int max_pairs(Kernel kernel, int threads, int smem, int sm_count) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = sm_count / 2;
+    }
+    return n < sm_count / 2 ? n : sm_count / 2;
+}
+
+template <int BN, int MODE, int BL>
+int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
+    using Cfg = PairCfg<BN, MODE, BL>;
+    auto kernel = gemm_a8w8_pair_sm100_kernel<Cfg>;
+    int rc = set_smem(kernel, Cfg::SMEM_BYTES);
+    if (rc) return rc;
+    static int pairs_cached[kMaxDevices] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (pairs_cached[dev] == 0) pairs_cached[dev] = max_pairs(kernel, Cfg::THREADS, Cfg::SMEM_BYTES, sm_count);
+    const int pairs = p.tiles_total < pairs_cached[dev] ? p.tiles_total : pairs_cached[dev];
+    kernel<<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+
+template <int BN>
+int launch_pair_modes(const b200_gemm_args* a, const GemmParams& p, int sm_count, cudaStream_t st) {
+    const bool flat = a->b_layout == B200_B_FLAT_16x16;
+    switch (a->scale_mode) {
+        case B200_SCALE_BLOCK:
+            return flat ? launch_pair<BN, MODE_BLOCK, BL_FLAT>(p, sm_count, st) : launch_pair<BN, MODE_BLOCK, BL_NK>(p, sm_count, st);
+        case B200_SCALE_MX:
+            if constexpr (BN == 256)
+                return flat ? launch_pair<BN, MODE_MX, BL_FLAT>(p, sm_count, st) : launch_pair<BN, MODE_MX, BL_NK>(p, sm_count, st);
+            else
+                return B200_ERR_UNSUPPORTED;
+        default:
+            return flat ? launch_pair<BN, MODE_ACC, BL_FLAT>(p, sm_count, st) : launch_pair<BN, MODE_ACC, BL_NK>(p, sm_count, st);
+    }
 }
 
 template <int MODE, int BL>
@@ -319,16 +406,37 @@ int run_decode(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStr
 }
 
 int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
-    const int BN = pl.tile == B200_TILE_128x256 ? 256 : 128;
+    int BN = 128;
+    bool pair = false;
+    switch (pl.tile) {
+        case B200_TILE_128x256: BN = 256; break;
+        case B200_TILE_PAIR_256x256: BN = 256; pair = true; break;
+        case B200_TILE_PAIR_256x224: BN = 224; pair = true; break;
+        case B200_TILE_PAIR_256x192: BN = 192; pair = true; break;
+        case B200_TILE_PAIR_256x128: BN = 128; pair = true; break;
+        default: BN = 128; break;
+    }
+    const int BMT = pair ? 256 : 128;                 // output rows per tile
+    const int BROWS = pair ? BN / 2 : BN;             // B rows one CTA loads
     GemmParams p;
     std::memset(&p, 0, sizeof(p));
     int rc = make_rowmajor_tmap(&p.tmap_a, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, 128);
     if (rc) return rc;
     if (a->b_layout == B200_B_NK_ROWMAJOR)
-        rc = make_rowmajor_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, BN);
+        rc = make_rowmajor_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, BROWS);
     else
-        rc = make_flat_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, BN);
+        rc = make_flat_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, BROWS);
     if (rc) return rc;
+    if (pair && a->scale_mode == B200_SCALE_MX) {
+        // scale atoms as rows of 256 bytes; one atom = 2 rows
+        const uint64_t bytes_a = a->batch > 1 ? static_cast<uint64_t>(a->stride_sfa_batch) * a->batch : b200_mx_sf_bytes(a->m, a->k);
+        const uint64_t bytes_b = a->batch > 1 ? static_cast<uint64_t>(a->stride_sfb_batch) * a->batch : b200_mx_sf_bytes(a->n, a->k);
+        const uint64_t da[2] = {256, bytes_a / 256}, db[2] = {256, bytes_b / 256};
+        const uint64_t str[1] = {256};
+        const uint32_t box_a[2] = {256, 2}, box_b[2] = {256, static_cast<uint32_t>(2 * ((BN + 127) / 128))};
+        if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 2, da, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+        if ((rc = make_tmap(&p.tmap_sfb, a->ptr_sfb, 2, db, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    }
     p.c = a->ptr_c;
     p.sfa = static_cast<const float*>(a->ptr_sfa);
     p.sfb = static_cast<const float*>(a->ptr_sfb);
@@ -340,7 +448,7 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
     p.n = static_cast<int>(a->n);
     p.k = static_cast<int>(a->k);
     p.batch = static_cast<int>(a->batch);
-    p.tiles_m = static_cast<int>((a->m + 127) / 128);
+    p.tiles_m = static_cast<int>((a->m + BMT - 1) / BMT);
     p.tiles_n = static_cast<int>((a->n + BN - 1) / BN);
     const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batch;
     if (total > 0x7FFFFFFF) return B200_ERR_TOO_LARGE;
@@ -359,6 +467,14 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         p.sfb_stride = a->stride_sfb;
         p.sfa_batch = a->stride_sfa_batch;
         p.sfb_batch = a->stride_sfb_batch;
+    }
+    if (pair) {
+        switch (BN) {
+            case 256: return launch_pair_modes<256>(a, p, ds->sm_count, st);
+            case 224: return launch_pair_modes<224>(a, p, ds->sm_count, st);
+            case 192: return launch_pair_modes<192>(a, p, ds->sm_count, st);
+            default: return launch_pair_modes<128>(a, p, ds->sm_count, st);
+        }
     }
     const int grid = p.tiles_total < ds->sm_count ? p.tiles_total : ds->sm_count;
     const bool flat = a->b_layout == B200_B_FLAT_16x16;

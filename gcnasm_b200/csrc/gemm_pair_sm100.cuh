@@ -1,0 +1,343 @@
+// A8W8 FP8 (E4M3) NT GEMM for sm_100a on CTA PAIRS: two CTAs on neighbouring SMs (a 2-CTA cluster)
+// compute one 256 x BN output tile with tcgen05.mma.cta_group::2.
+//
+// Why pairs: the tensor pipe retires a 128x256x128 block in about 512 clocks, and a single CTA has to
+// pull 48 KB (A 16 KB + B 32 KB) out of L2 for it -- more than the L2->SM path sustains.  In a pair each CTA
+// loads its own 128 A rows and only HALF of the B rows (BN/2); the hardware reads both halves of B
+// from the two CTAs' shared memories.  Per CTA that is 16 + 16 KB per block instead of 48 KB.  No load is
+// ever shared between CTAs by multicast; each CTA issues plain TMA loads for its own bytes.
+//
+// Roles per CTA (12 warps, same split as the single-CTA kernel): warp 0 TMA producer, warp 1 UMMA issuer
+// (only the pair's leader, cluster rank 0, issues MMAs; it also frees ring stages in BOTH CTAs), warps
+// 4-11 epilogue.  Block-scale mode keeps the reference's structure (a fresh accumulator per 128-wide K
+// group, gemm_a8w8_blockscale_kernel_template.hpp:317,334; scale_c_tile :24-39): partials ping-pong
+// between two TMEM buffers and are folded into register accumulators with packed fp32 FMAs.
+#pragma once
+
+#include "gemm_sm100.cuh"
+
+namespace b200 {
+
+template <int BN_, int MODE_, int BLAYOUT_>
+struct PairCfg {
+    static constexpr int BM = 128, BN = BN_, BK = 128, MODE = MODE_, BLAYOUT = BLAYOUT_;
+    static constexpr int BH = BN / 2;                               // B rows loaded by each CTA
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = BH * BK;
+    static constexpr int SFB_ATOMS = (BN + 127) / 128;
+    static constexpr int SFA_BYTES = (MODE == MODE_MX) ? 512 : 0;
+    static constexpr int SFB_BYTES = (MODE == MODE_MX) ? SFB_ATOMS * 512 : 0;
+    static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
+    static constexpr int STAGES_RAW = (225 * 1024 - 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024;
+    static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
+    static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
+    static constexpr int ACC_COLS = ACC_STAGES * BN;
+    static constexpr int TMEM_COLS = (ACC_COLS + SF_COLS) <= 128 ? 128 : (ACC_COLS + SF_COLS) <= 256 ? 256 : 512;
+    static constexpr int NCH = BN / 2;                              // columns owned by one epilogue thread
+    static constexpr int THREADS = 384;
+    static_assert(BN % 32 == 0 && BN <= 256 && BN >= 64, "pair tile N: multiple of 32 in [64, 256]");
+    static_assert(MODE != MODE_BLOCK || ACC_STAGES == 2, "block-scale needs two partial buffers");
+    static_assert(MODE != MODE_MX || BN % 128 == 0, "MX scale atoms cover 128 columns");
+    static_assert(ACC_COLS + SF_COLS <= 512, "TMEM overflow");
+};
+
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    return static_cast<unsigned long long>(__float_as_uint(lo)) | (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+}
+// d = a * b + c on two packed fp32 lanes
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+template <class Cfg>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::THREADS, 1)
+gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, BH = Cfg::BH, STAGES = Cfg::STAGES, MODE = Cfg::MODE;
+    constexpr int NCH = Cfg::NCH, ACC_STAGES = Cfg::ACC_STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
+    const uint32_t bar_full0 = smem_base + STAGES * Cfg::STAGE_BYTES;   // used in the leader only
+    const uint32_t bar_empty0 = bar_full0 + STAGES * 8;                 // one set per CTA
+    const uint32_t bar_accf0 = bar_empty0 + STAGES * 8;                 // one set per CTA
+    const uint32_t bar_acce0 = bar_accf0 + 2 * 8;                       // used in the leader only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();          // 0 = leader
+    const uint32_t peer = cta ^ 1u;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full0 + s * 8, 1);          // leader's arrive.expect_tx; bytes from both CTAs
+            mbar_init(bar_empty0 + s * 8, 1);         // one tcgen05.commit per use
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_accf0 + s * 8, 1);          // one tcgen05.commit per use
+            mbar_init(bar_acce0 + s * 8, 16);         // 8 epilogue warps in each of the two CTAs
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&p.tmap_a);
+        prefetch_tmap(&p.tmap_b);
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs' barriers must exist before either CTA signals the other
+    cluster_arrive();
+    cluster_wait();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // cta_group::2 MMAs write the same TMEM address in both CTAs: the two allocations must agree
+    const bool tmem_ok = ld_shared_cluster_u32(mapa_shared(smem_u32(tmem_slot), peer)) == tmem_base;
+    if (!tmem_ok && threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, KSTAT_TMEM_MISMATCH);
+
+    const int groups = (MODE == MODE_BLOCK) ? p.kblocks : 1;
+    const int kb_per_group = (MODE == MODE_BLOCK) ? 1 : p.kblocks;
+
+    if (!tmem_ok) {
+        // fall through to the teardown
+    } else if (warp < 4) {
+        setmaxnreg_dec<40>();
+        if (warp == 0 && lane == 0) {
+            // ------------------------------ TMA producer (both CTAs) ------------------------------
+            uint32_t it = 0;
+            bool ok = true;
+            const uint32_t leader_full0 = mapa_shared(bar_full0, 0);
+            for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
+                int b, mi, ni;
+                tile_coords(p, t, b, mi, ni);
+                const int row_a = mi * (2 * BM) + static_cast<int>(cta) * BM;
+                const int row_b = ni * BN + static_cast<int>(cta) * BH;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait<true>(bar_empty0 + s * 8, ph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    if (cta == 0)
+                        mbar_arrive_expect_tx(bar_full0 + s * 8,
+                                              2 * (Cfg::A_BYTES + Cfg::B_BYTES + Cfg::SFA_BYTES + Cfg::SFB_BYTES));
+                    const uint32_t full = leader_full0 + s * 8;
+                    tma_load_3d_pair(sa, &p.tmap_a, full, kb * BK, row_a, b);
+                    if constexpr (Cfg::BLAYOUT == BL_NK)
+                        tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, b);
+                    else
+                        tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), b);
+                    if constexpr (MODE == MODE_MX) {
+                        // scale atoms [batch][K/128][rows/128][512 B], addressed as rows of 256 bytes
+                        const long long atom_a = b * (p.sfa_batch >> 9) + static_cast<long long>(kb) * p.sfa_stride + (mi * 2 + cta);
+                        const long long atom_b = b * (p.sfb_batch >> 9) + static_cast<long long>(kb) * p.sfb_stride + ni * Cfg::SFB_ATOMS;
+                        tma_load_2d_pair(sb + Cfg::B_BYTES, &p.tmap_sfa, full, 0, static_cast<int>(atom_a * 2));
+                        tma_load_2d_pair(sb + Cfg::B_BYTES + 512, &p.tmap_sfb, full, 0, static_cast<int>(atom_b * 2));
+                    }
+                }
+            }
+        } else if (warp == 1 && lane == 0 && cta == 0) {
+            // ------------------------------ UMMA issuer (leader only) ------------------------------
+            uint32_t it = 0, phase = 0;
+            bool ok = true;
+            constexpr uint32_t idesc = make_idesc_f8(2 * BM, BN);
+            for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
+                for (int g = 0; g < groups && ok; ++g, ++phase) {
+                    const uint32_t as = phase % ACC_STAGES;
+                    const uint32_t aph = (phase / ACC_STAGES) & 1;
+                    if (!mbar_wait<true>(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t tacc = tmem_base + as * BN;
+                    for (int kb = 0; kb < kb_per_group; ++kb, ++it) {
+                        const uint32_t s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!mbar_wait<true>(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
+                        const uint32_t sb = sa + Cfg::A_BYTES;
+                        if constexpr (MODE == MODE_MX) {
+                            const uint32_t tsf = tmem_base + Cfg::ACC_COLS;
+                            tmem_cp_sf<2>(tsf, make_smem_desc(sb + Cfg::B_BYTES, 0, 128, kSwizzleNone));
+#pragma unroll
+                            for (int a = 0; a < Cfg::SFB_ATOMS; ++a)
+                                tmem_cp_sf<2>(tsf + 4 + 4 * a,
+                                              make_smem_desc(sb + Cfg::B_BYTES + 512 + 512 * a, 0, 128, kSwizzleNone));
+                        }
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k) {
+                            const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, kSwizzle128B);
+                            uint64_t db;
+                            if constexpr (Cfg::BLAYOUT == BL_NK) {
+                                db = make_smem_desc(sb + k * 32, 16, 1024, kSwizzle128B);
+                            } else {
+                                constexpr uint32_t LBO = (BH / 16) * 256;
+                                db = make_smem_desc(sb + k * 2 * LBO, LBO, 128, kSwizzleNone);
+                            }
+                            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                            if constexpr (MODE == MODE_MX) {
+                                const uint32_t tsf = tmem_base + Cfg::ACC_COLS;
+                                umma_mxf8<2>(tacc, da, db, make_idesc_mxf8(2 * BM, BN, k, k), accum, tsf, tsf + 4);
+                            } else {
+                                umma_f8<2>(tacc, da, db, idesc, accum);
+                            }
+                        }
+                        umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
+                    }
+                    if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs
+                }
+            }
+        }
+    } else {
+        // ---------------------------------- epilogue (both CTAs) ----------------------------------
+        setmaxnreg_inc<216>();
+        const int ew = warp - 4;
+        const int quad = warp & 3;
+        const int half = ew >> 2;
+        const int row_in_tile = static_cast<int>(cta) * BM + quad * 32 + lane;
+        const uint32_t tmem_lane = static_cast<uint32_t>(quad * 32) << 16;
+        const size_t esz = (p.out_dtype == OUT_BF16) ? 2 : 4;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && ((p.ldc * esz) % 16 == 0) &&
+                            ((p.c_batch * esz) % 16 == 0);
+        const uint32_t leader_acce0 = mapa_shared(bar_acce0, 0);
+        float tscale = 1.0f;
+        if constexpr (MODE == MODE_ACC) {
+            if (p.scale_a) tscale *= __ldg(p.scale_a);
+            if (p.scale_b) tscale *= __ldg(p.scale_b);
+        }
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
+            int b, mi, ni;
+            tile_coords(p, t, b, mi, ni);
+            const int row = mi * (2 * BM) + row_in_tile;
+            const int col_base = ni * BN + half * NCH;
+            uint8_t* crow = reinterpret_cast<uint8_t*>(p.c) +
+                            (static_cast<size_t>(b) * p.c_batch + static_cast<size_t>(row) * p.ldc) * esz;
+
+            if constexpr (MODE == MODE_BLOCK) {
+                unsigned long long acc[NCH / 2];
+#pragma unroll
+                for (int j = 0; j < NCH / 2; ++j) acc[j] = 0ull;
+                // this thread's NCH columns touch at most two 128-wide scale blocks of B
+                const int blk0 = col_base >> 7;
+                const int split = ((blk0 + 1) << 7) - col_base;          // columns before the block boundary
+                const bool has1 = split < NCH && ((blk0 + 1) << 7) < p.n;
+                const bool col_ok = col_base < p.n;
+                const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
+                const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(blk0) * p.sfb_stride;
+                float sa_next = __ldg(sfa_p);
+                float sb0_next = col_ok ? __ldg(sfb_p) : 0.0f;
+                float sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
+                for (int g = 0; g < groups; ++g, ++phase) {
+                    const float s0 = sa_next * sb0_next, s1 = sa_next * sb1_next;
+                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = pack_f32x2(s1, s1);
+                    if (g + 1 < groups) {
+                        sa_next = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
+                        sb0_next = col_ok ? __ldg(sfb_p + g + 1) : 0.0f;
+                        sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
+                    }
+                    const uint32_t as = phase & 1;
+                    const uint32_t aph = (phase >> 1) & 1;
+                    if (!mbar_wait<true>(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
+                    // 16-column chunks, two in flight
+                    float v[2][16];
+                    tmem_ld16(taddr, v[0]);
+#pragma unroll
+                    for (int c = 0; c < NCH / 16; ++c) {
+                        tmem_ld_wait();
+                        if (c + 1 < NCH / 16) tmem_ld16(taddr + (c + 1) * 16, v[(c + 1) & 1]);
+                        const unsigned long long sc = (c * 16 < split) ? sc0 : sc1;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            acc[c * 8 + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), sc, acc[c * 8 + j]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                }
+                if (ok && row < p.m) {
+#pragma unroll
+                    for (int c = 0; c < NCH / 16; ++c) {
+                        float o[16];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            o[2 * j] = __uint_as_float(static_cast<uint32_t>(acc[c * 8 + j]));
+                            o[2 * j + 1] = __uint_as_float(static_cast<uint32_t>(acc[c * 8 + j] >> 32));
+                        }
+                        store_row_chunk<16>(p, crow, col_base + c * 16, o, vec_ok);
+                    }
+                }
+            } else {
+                const uint32_t as = phase % ACC_STAGES;
+                const uint32_t aph = (phase / ACC_STAGES) & 1;
+                if (!mbar_wait<true>(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
+                constexpr int CW = (NCH % 32 == 0) ? 32 : 16;      // columns per TMEM load
+                constexpr int NC = NCH / CW;
+                float v[2][CW];
+                tmem_ld<CW>(taddr, v[0]);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    tmem_ld_wait();
+                    if (c + 1 < NC) tmem_ld<CW>(taddr + (c + 1) * CW, v[(c + 1) & 1]);
+                    if (c + 1 == NC) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                    }
+                    if (MODE == MODE_ACC) {
+#pragma unroll
+                        for (int j = 0; j < CW; ++j) v[c & 1][j] *= tscale;
+                    }
+                    if (row < p.m) store_row_chunk<CW>(p, crow, col_base + c * CW, v[c & 1], vec_ok);
+                }
+                ++phase;
+            }
+        }
+    }
+
+    // ---------------------------------- teardown ----------------------------------
+    tc_fence_before();
+    __syncthreads();
+    // neither CTA may leave while its partner can still read its shared memory or signal its barriers
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace b200

@@ -27,6 +27,8 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1 };
 struct GemmParams {
     CUtensorMap tmap_a;          // u8 [batch][M][K], box 128 x 128, 128-byte swizzle
     CUtensorMap tmap_b;          // u8 [batch][N][K] (same box) or the flat 4-D view
+    CUtensorMap tmap_sfa;        // pair kernels, MX only: scale atoms as u8 [atoms*2][256], box 256 x 2
+    CUtensorMap tmap_sfb;        //                                                       box 256 x 2*atoms
     void* c;
     const float* sfa;            // block: fp32 [K/128][M];   MX: E8M0 atoms (uint8, see sf_relayout)
     const float* sfb;            // block: fp32 [N/128][K/128]; MX: E8M0 atoms

@@ -17,6 +17,7 @@ enum : int {
     KSTAT_TIMEOUT_ACC_F = 3,   // epilogue gave up waiting for an accumulator
     KSTAT_TIMEOUT_ACC_E = 4,   // MMA issuer gave up waiting for a drained accumulator
     KSTAT_TIMEOUT_PEER  = 5,   // wait on the partner CTA of a pair expired
+    KSTAT_TMEM_MISMATCH = 6,   // the two CTAs of a pair got different TMEM base addresses
 };
 
 // Wall-clock budget of one wait.  A wait that exceeds it records a status code, raises the
@@ -140,6 +141,12 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap,
     asm volatile(
         "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
 // linear bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16
@@ -278,6 +285,18 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     else
         asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Pair kernels: arrive on the barrier at offset `bar` in BOTH CTAs of the pair once the MMAs issued so far
+// have completed.  Two plain commits, one per CTA; the partner's barrier is named by its mapa address.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint32_t b0 = mapa_shared(bar, 0), b1 = mapa_shared(bar, 1);
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b0) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b1) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
 // shared memory -> TMEM copy of one 32-row x 16-byte scale-factor atom, replicated into the
 // four 32-lane quadrants
 template <int kCtaGroup>
@@ -311,6 +330,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+template <int kCols>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float* v) {
+    static_assert(kCols == 16 || kCols == 32, "16 or 32 columns per load");
+    if constexpr (kCols == 16) tmem_ld16(taddr, v);
+    else tmem_ld32(taddr, v);
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

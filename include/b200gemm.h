@@ -32,7 +32,8 @@ enum b200_b_layout {
 enum b200_out_dtype { B200_OUT_F32 = 0, B200_OUT_BF16 = 1 };
 enum b200_tile_hint {
     B200_TILE_AUTO = 0, B200_TILE_128x128 = 1, B200_TILE_128x256 = 2, B200_TILE_DECODE = 3,
-    B200_TILE_PAIR_256x256 = 4, B200_TILE_128x64 = 5, B200_TILE_PAIR_256x128 = 6
+    B200_TILE_PAIR_256x256 = 4, B200_TILE_128x64 = 5 /* reserved */, B200_TILE_PAIR_256x128 = 6,
+    B200_TILE_PAIR_256x224 = 7, B200_TILE_PAIR_256x192 = 8   /* PAIR_*: two CTAs share a 256-row tile */
 };
 enum b200_error {
     B200_OK = 0,

@@ -65,7 +65,7 @@ def test_validation_codes(native):
 
     tile = C.c_int32(0)
     chk = lambda a: native.b200_gemm_check(C.byref(a), C.byref(tile))
-    assert chk(_args()) == L.OK and tile.value in (L.TILE_128x128, L.TILE_128x256)
+    assert chk(_args()) == L.OK and tile.value in (L.TILE_128x128, L.TILE_128x256, L.TILE_PAIR_256x128)
     assert native.b200_gemm_check(None, None) == L.ERR_BAD_ARG
     assert chk(_args(ptr_a=0)) == L.ERR_BAD_ARG
     # non-positive sizes are rejected like the reference's "Invalid problem size" (gemm_a8w8_8wave.cc:685-688)
@@ -90,10 +90,12 @@ def test_validation_codes(native):
     assert chk(_args(m=16)) == L.OK and tile.value == L.TILE_DECODE
     assert chk(_args(**{**bs, "m": 64, "stride_sfa": 64})) == L.OK and tile.value == L.TILE_DECODE
     assert chk(_args(m=65)) == L.OK and tile.value != L.TILE_DECODE
-    assert chk(_args(m=4096, n=7168, k=2048, stride_a=2048, stride_b=2048, stride_c=7168)) == L.OK and tile.value == L.TILE_128x256
+    assert chk(_args(m=4096, n=7168, k=2048, stride_a=2048, stride_b=2048, stride_c=7168)) == L.OK and tile.value == L.TILE_PAIR_256x224
+    assert chk(_args(m=8192, n=8192, k=8192, stride_a=8192, stride_b=8192, stride_c=8192)) == L.OK and tile.value == L.TILE_PAIR_256x256
     assert chk(_args(m=128, tile_hint=L.TILE_DECODE)) == L.ERR_UNSUPPORTED
     mx = dict(scale_mode=L.SCALE_MX, ptr_sfa=0x4000, ptr_sfb=0x5000)
-    assert chk(_args(**mx)) == L.OK and tile.value == L.TILE_128x128
+    assert chk(_args(**mx)) == L.OK and tile.value in (L.TILE_128x128, L.TILE_PAIR_256x256)
+    assert chk(_args(**mx, tile_hint=L.TILE_128x256)) == L.ERR_UNSUPPORTED
     assert chk(_args(**mx, k=1056, stride_a=1056, stride_b=1056)) == L.ERR_UNSUPPORTED
 
 

@@ -27,7 +27,7 @@ def config2(api, O):
     return m, n, k, qa, qb, sfa, sfb
 
 
-@pytest.mark.parametrize("tile", [1, 2])
+@pytest.mark.parametrize("tile", [2, 4, 7])
 def test_config2_blockscale_full(api, O, config2, tile):
     m, n, k, qa, qb, sfa, sfb = config2
     c = api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out_dtype=torch.bfloat16, tile=tile)

@@ -30,7 +30,7 @@ NT_SHAPES = [(256, 512, 256), (256, 512, 1024), (128, 128, 128), (200, 136, 144)
              (65, 16, 16), (300, 400, 272)]
 
 
-@pytest.mark.parametrize("tile", [1, 2])
+@pytest.mark.parametrize("tile", [1, 2, 4, 6, 7, 8])
 @pytest.mark.parametrize("m,n,k", NT_SHAPES)
 def test_nt_unscaled_fp32(api, O, m, n, k, tile):
     a = e4m3(O, (m, k), 1, 0, 0.0, 1.0)
@@ -64,7 +64,7 @@ def test_nt_batched(api, O):
     B, m, n, k = 8, 256, 512, 256
     a = e4m3(O, (B, m, k), 5, 0, 0.0, 1.0)
     b = e4m3(O, (B, n, k), 5, 1, -0.5, 0.5)
-    for tile in (1, 2):
+    for tile in (1, 2, 4, 7):
         c = api.gemm_a8w8(T(a), T(b), out_dtype=torch.float32, tile=tile).cpu().numpy()
         status_ok(api)
         for i in range(B):
@@ -86,7 +86,11 @@ def test_nt_strided_views(api, O):
 
 
 BS_SHAPES = [(128, 128, 256, 1), (256, 512, 1024, 1), (128, 256, 256, 2), (384, 640, 1024, 2), (77, 384, 512, 2),
-             (2048, 4096, 1024, 2), (130, 128, 128, 1)]
+             (2048, 4096, 1024, 2), (130, 128, 128, 1),
+             # CTA-pair tiles: 256x256, 256x128, 256x224 (tiles straddle the 128-column scale blocks), 256x192
+             (256, 256, 256, 4), (512, 768, 1024, 4), (300, 640, 512, 4), (2048, 4096, 1024, 4), (77, 384, 512, 4),
+             (512, 768, 1024, 6), (512, 896, 1024, 7), (300, 640, 512, 7), (2048, 3584, 1024, 7), (512, 768, 1024, 8),
+             (1000, 1152, 384, 8), (4096, 7168, 256, 0)]
 
 
 @pytest.mark.parametrize("m,n,k,tile", BS_SHAPES)
@@ -113,11 +117,11 @@ def test_blockscale_quantised_normal_bf16(api, O):
     xb = O.fill_normal((n, k), 1234, 1)
     qa, sfa = O.quant_1x128(xa)
     qb, sfb = O.quant_128x128(xb)
-    for tile in (1, 2):
+    ref = O.bf16_bits_to_f32(O.gemm_ref_blockscale(qa, qb, sfa, sfb, out_bf16=True))
+    for tile in (1, 2, 4, 6, 7, 8):
         c = api.gemm_a8w8_blockscale(T(qa), T(qb), T(sfa), T(sfb), out_dtype=torch.bfloat16, tile=tile)
         status_ok(api)
-        ref = O.bf16_bits_to_f32(O.gemm_ref_blockscale(qa, qb, sfa, sfb, out_bf16=True))
-        assert_close(O, c.float().cpu().numpy(), ref, "config-2 recipe")
+        assert_close(O, c.float().cpu().numpy(), ref, f"config-2 recipe tile {tile}")
     full = xa.astype(np.float64) @ xb.astype(np.float64).T
     assert np.max(np.abs(c.float().cpu().numpy() - full)) <= 0.05 * np.max(np.abs(full))
 
@@ -134,7 +138,8 @@ def test_blockscale_batched(api, O):
         assert_close(O, c[i], O.gemm_ref_blockscale(a[i], b[i], sfa[i], sfb[i]), f"batch {i}")
 
 
-@pytest.mark.parametrize("m,n,k,tile", [(256, 512, 256, 1), (200, 272, 384, 2), (256, 512, 256, 2), (96, 1024, 1024, 0)])
+@pytest.mark.parametrize("m,n,k,tile", [(256, 512, 256, 1), (200, 272, 384, 2), (256, 512, 256, 2), (96, 1024, 1024, 0),
+                                        (256, 512, 256, 4), (300, 672, 384, 7), (512, 384, 256, 8), (256, 512, 256, 6)])
 def test_flatmm_reference_semantics(api, O, m, n, k, tile):
     """flatmm_a8w8: B created as [K,N], shuffled, host check on the unshuffled matrix, threshold 0.1
     (opus_fmm/flatmm_a8w8_gfx950.cc:732-742,586-597,798)."""
@@ -167,7 +172,7 @@ def test_flat_blockscale(api, O):
     sfa = O.fill_uniform((k // 128, m), 9, 2, 0.8, 1.2)
     sfb = O.fill_uniform((n // 128, k // 128), 9, 3, 0.8, 1.2)
     flat = api.shuffle_b(T(b), "nk")
-    for tile in (1, 2):
+    for tile in (1, 2, 4, 7):
         c = api.gemm_a8w8_blockscale(T(a), flat, T(sfa), T(sfb), out_dtype=torch.float32, tile=tile, b_flat_n=n)
         status_ok(api)
         assert_close(O, c.cpu().numpy(), O.gemm_ref_blockscale(a, b, sfa, sfb), "flat block")
@@ -183,9 +188,10 @@ def test_mxfp8(api, O, m, n, k):
     sa = api.mx_sf_relayout(T(ea), m, k)
     sb = api.mx_sf_relayout(T(eb), n, k)
     ref = O.gemm_ref_mx(qa, qb, ea, eb)
-    c = api.gemm_a8w8_mx(T(qa), T(qb), sa, sb, out_dtype=torch.float32)
-    status_ok(api)
-    assert_close(O, c.cpu().numpy(), ref, "mx")
+    for tile in (1, 4, 0):
+        c = api.gemm_a8w8_mx(T(qa), T(qb), sa, sb, out_dtype=torch.float32, tile=tile)
+        status_ok(api)
+        assert_close(O, c.cpu().numpy(), ref, f"mx tile {tile}")
     cb = api.gemm_a8w8_mx(T(qa), T(qb), sa, sb, out_dtype=torch.bfloat16)
     status_ok(api)
     assert_close(O, cb.float().cpu().numpy(), O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref)), "mx bf16")
@@ -239,8 +245,11 @@ def test_error_behaviour_on_device(api, O):
 
     a = T(e4m3(O, (128, 128), 1, 0, 0, 1))
     b = T(e4m3(O, (100, 128), 1, 1, 0, 1))
-    with pytest.raises(B200Error):                          # block scale needs N % 128 == 0
-        api.gemm_a8w8_blockscale(a, b, torch.ones(1, 128, device=DEV), torch.ones(1, 1, device=DEV))
+    with pytest.raises(B200Error) as ei:                    # K = 24 is not a multiple of 16: TMA row pitch
+        api.gemm_a8w8(T(e4m3(O, (128, 24), 1, 0, 0, 1)), T(e4m3(O, (100, 24), 1, 1, 0, 1)))
+    assert ei.value.code == -2
+    with pytest.raises(B200Error):                          # flat layout needs K % 128 == 0
+        api.flatmm_a8w8(T(e4m3(O, (128, 64), 1, 0, 0, 1)), T(e4m3(O, (64 * 128,), 1, 1, 0, 1)), 128)
     with pytest.raises(TypeError):
         api.gemm_a8w8(a.float(), b)
     with pytest.raises(ValueError):
