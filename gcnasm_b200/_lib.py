@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libb200gemm.so")
+# B200GEMM_LIB overrides the in-tree library path (e.g. an instrumented build)
+LIB_PATH = os.environ.get("B200GEMM_LIB") or os.path.join(_PKG, "libb200gemm.so")
 
 # enums (include/b200gemm.h)
 SCALE_NONE, SCALE_TENSOR, SCALE_BLOCK, SCALE_MX = 0, 1, 2, 3

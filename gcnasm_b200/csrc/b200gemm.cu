@@ -807,6 +807,13 @@ int b200_release(void) {
     return B200_OK;
 }
 const char* b200_version(void) { return "b200gemm 0.1 (sm_100a)"; }
+#ifdef B200_TRACE
+int b200_trace_read(long long* host, int count) {
+    CU_TRY(cudaDeviceSynchronize());
+    CU_TRY(cudaMemcpyFromSymbol(host, b200::g_trace, sizeof(long long) * count));
+    return 0;
+}
+#endif
 uint64_t b200_launch_count(void) { return g_launches.load(); }
 
 }  // extern "C"

@@ -53,6 +53,21 @@ __device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsign
     return d;
 }
 
+#ifdef B200_TRACE
+__device__ long long g_trace[16384];
+#define B200_TRACE_EPI(slot)                                                                     \
+    do {                                                                                         \
+        if (pair_id == 0 && cta == 0 && warp == 4 && lane == 0 && phase < 1024) g_trace[phase * 4 + (slot)] = clock64(); \
+    } while (0)
+#define B200_TRACE_MMA(slot)                                                                     \
+    do {                                                                                         \
+        if (pair_id == 0 && phase < 1024) g_trace[8192 + phase * 4 + (slot)] = clock64();         \
+    } while (0)
+#else
+#define B200_TRACE_EPI(slot)
+#define B200_TRACE_MMA(slot)
+#endif
+
 template <class Cfg>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::THREADS, 1)
 gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
@@ -162,10 +177,12 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 for (int g = 0; g < groups && ok; ++g, ++phase) {
                     const uint32_t as = phase % ACC_STAGES;
                     const uint32_t aph = (phase / ACC_STAGES) & 1;
+                    B200_TRACE_MMA(0);
                     if (!mbar_wait<true>(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
                         ok = false;
                         break;
                     }
+                    B200_TRACE_MMA(1);
                     tc_fence_after();
                     const uint32_t tacc = tmem_base + as * BN;
                     for (int kb = 0; kb < kb_per_group; ++kb, ++it) {
@@ -175,6 +192,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             ok = false;
                             break;
                         }
+                        B200_TRACE_MMA(2);
                         tc_fence_after();
                         const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
                         const uint32_t sb = sa + Cfg::A_BYTES;
@@ -207,12 +225,13 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
                     }
                     if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs
+                    B200_TRACE_MMA(3);
                 }
             }
         }
     } else {
         // ---------------------------------- epilogue (both CTAs) ----------------------------------
-        setmaxnreg_inc<216>();
+        setmaxnreg_inc<232>();
         const int ew = warp - 4;
         const int quad = warp & 3;
         const int half = ew >> 2;
@@ -242,9 +261,11 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                 for (int j = 0; j < NCH / 2; ++j) acc[j] = 0ull;
                 // this thread's NCH columns touch at most two 128-wide scale blocks of B
+                // (with BN = 256 every thread's 128 columns are exactly one block: no second scale)
+                constexpr bool kStraddle = (BN % 256) != 0;
                 const int blk0 = col_base >> 7;
-                const int split = ((blk0 + 1) << 7) - col_base;          // columns before the block boundary
-                const bool has1 = split < NCH && ((blk0 + 1) << 7) < p.n;
+                const int split = kStraddle ? ((blk0 + 1) << 7) - col_base : NCH;   // columns before the block boundary
+                const bool has1 = kStraddle && split < NCH && ((blk0 + 1) << 7) < p.n;
                 const bool col_ok = col_base < p.n;
                 const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
                 const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(blk0) * p.sfb_stride;
@@ -252,12 +273,12 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 float sb0_next = col_ok ? __ldg(sfb_p) : 0.0f;
                 float sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
                 for (int g = 0; g < groups; ++g, ++phase) {
-                    const float s0 = sa_next * sb0_next, s1 = sa_next * sb1_next;
-                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = pack_f32x2(s1, s1);
+                    const float s0 = sa_next * sb0_next, s1 = kStraddle ? sa_next * sb1_next : s0;
+                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
                     if (g + 1 < groups) {
                         sa_next = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
                         sb0_next = col_ok ? __ldg(sfb_p + g + 1) : 0.0f;
-                        sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
+                        if (kStraddle) sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
                     }
                     const uint32_t as = phase & 1;
                     const uint32_t aph = (phase >> 1) & 1;
@@ -267,21 +288,46 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
-                    // 16-column chunks, two in flight
-                    float v[2][16];
-                    tmem_ld16(taddr, v[0]);
+                    B200_TRACE_EPI(0);
+                    // 32-column loads, one load ahead of the FMAs; a 16-column tail when NCH % 32 != 0.
+                    // The buffer goes back to the MMA issuer as soon as the last load has landed.
+                    constexpr int C32 = NCH / 32, TAIL = NCH % 32;
+                    float v[2][32];
+                    tmem_ld32(taddr, v[0]);
 #pragma unroll
-                    for (int c = 0; c < NCH / 16; ++c) {
+                    for (int c = 0; c < C32; ++c) {
                         tmem_ld_wait();
-                        if (c + 1 < NCH / 16) tmem_ld16(taddr + (c + 1) * 16, v[(c + 1) & 1]);
-                        const unsigned long long sc = (c * 16 < split) ? sc0 : sc1;
+                        if (c + 1 < C32) {
+                            tmem_ld32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+                        } else if (TAIL) {
+                            tmem_ld16(taddr + C32 * 32, v[(c + 1) & 1]);
+                        } else {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                            B200_TRACE_EPI(1);
+                        }
+                        const unsigned long long scA = (!kStraddle || c * 32 < split) ? sc0 : sc1;
+                        const unsigned long long scB = (!kStraddle || c * 32 + 16 < split) ? sc0 : sc1;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            acc[c * 8 + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), sc, acc[c * 8 + j]);
+                            acc[c * 16 + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), scA, acc[c * 16 + j]);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                    if (TAIL) {
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                        B200_TRACE_EPI(1);
+                        const unsigned long long scT = (!kStraddle || C32 * 32 < split) ? sc0 : sc1;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            acc[C32 * 16 + j] = ffma2(pack_f32x2(v[C32 & 1][2 * j], v[C32 & 1][2 * j + 1]), scT, acc[C32 * 16 + j]);
+                    }
+                    B200_TRACE_EPI(2);
                 }
                 if (ok && row < p.m) {
 #pragma unroll

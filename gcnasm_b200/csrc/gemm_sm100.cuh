@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_a8w8_sm100_kernel(const 
         }
     } else {
         // ---------------------------------- epilogue ----------------------------------
-        setmaxnreg_inc<216>();
+        setmaxnreg_inc<232>();
         const int ew = warp - 4;
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
         const int half = ew >> 2;                  // which BN/2 column range

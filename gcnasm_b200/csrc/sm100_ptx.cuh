@@ -89,18 +89,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     return ok;
 }
 
-// Bounded wait.  `abort_flag` is a CTA-shared int; `status` the device status word.
+// Bounded wait.  `abort_flag` is a CTA-shared int; `status` the device status word.  The fast path is a
+// bare try_wait loop (each try_wait already suspends the thread for a hardware-defined interval); only a
+// wait that has failed many times starts reading the wall clock and checking the abort flag.
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-    if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0x3Fu) == 0) {
+        if ((++spins & 0xFFu) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitBudgetNs) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;
