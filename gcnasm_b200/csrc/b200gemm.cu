@@ -89,7 +89,7 @@ int device_state(DeviceState** out) {
 
 // u8 tensor map of rank `rank`; dims/strides innermost first, strides[i] = byte stride of dim i+1
 int make_tmap(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-              const uint32_t* box, CUtensorMapSwizzle swz) {
+              const uint32_t* box, CUtensorMapSwizzle swz, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
     cuuint64_t gd[5], gs[4];
     cuuint32_t bx[5], es[5];
     for (int i = 0; i < rank; ++i) {
@@ -98,7 +98,7 @@ int make_tmap(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
         es[i] = 1;
     }
     for (int i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
-    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gd,
+    CUresult r = g_encode(tm, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gd,
                           gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -436,6 +436,16 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         const uint32_t box_a[2] = {256, 2}, box_b[2] = {256, static_cast<uint32_t>(2 * ((BN + 127) / 128))};
         if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 2, da, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
         if ((rc = make_tmap(&p.tmap_sfb, a->ptr_sfb, 2, db, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    }
+    if (pair && a->scale_mode == B200_SCALE_BLOCK && aligned16(a->ptr_sfa) && a->stride_sfa % 4 == 0 &&
+        (a->batch == 1 || a->stride_sfa_batch % 4 == 0)) {
+        // fp32 SFA [batch][K/128][M] for the producer's per-group 128-row slices
+        const uint64_t d[3] = {static_cast<uint64_t>(a->m), static_cast<uint64_t>(a->k / 128), static_cast<uint64_t>(a->batch)};
+        const uint64_t st[2] = {static_cast<uint64_t>(a->stride_sfa) * 4,
+                                static_cast<uint64_t>(a->batch > 1 ? a->stride_sfa_batch : a->stride_sfa * (a->k / 128)) * 4};
+        const uint32_t bx[3] = {128, 1, 1};
+        if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 3, d, st, bx, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32))) return rc;
+        p.sfa_tma = 1;
     }
     p.c = a->ptr_c;
     p.sfa = static_cast<const float*>(a->ptr_sfa);

@@ -30,7 +30,9 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
     static constexpr int STAGES_RAW = (225 * 1024 - 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024;
+    static constexpr int SFA_RING = 2 * STAGES;                     // block-scale: slots of 128 fp32 A scales
+    static constexpr int SFA_RING_BYTES = (MODE == MODE_BLOCK) ? SFA_RING * 512 : 0;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + 1024;
     static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
     static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
     static constexpr int ACC_COLS = ACC_STAGES * BN;
@@ -44,24 +46,79 @@ struct PairCfg {
 };
 
 __device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
-    return static_cast<unsigned long long>(__float_as_uint(lo)) | (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+    unsigned long long d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 // d = a * b + c on two packed fp32 lanes
 __device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+#ifdef B200_SCALAR_FMA
+    float a0, a1, b0, b1, c0, c1;
+    unpack_f32x2(a, a0, a1);
+    unpack_f32x2(b, b0, b1);
+    unpack_f32x2(c, c0, c1);
+    return pack_f32x2(fmaf(a0, b0, c0), fmaf(a1, b1, c1));
+#else
     unsigned long long d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
+#endif
 }
 
+// Wait flavours per role (see mbar_wait / mbar_wait_poll): 1 = poll with a short sleep, 0 = suspending try_wait.
+// All waits use the default (CTA-scope) acquire even when the arrivals come from the partner CTA: a
+// cluster-scope acquire was measured at ~430 clocks per wait, and every hand-off here is ordered through the
+// async proxy (TMA complete_tx, tcgen05.commit) or tcgen05.fence, not through generic-proxy memory.
+#ifndef B200_PACE_NS
+#define B200_PACE_NS 0
+#endif
+#ifndef B200_PACE_COMMIT_NS
+#define B200_PACE_COMMIT_NS 80
+#endif
+#ifndef B200_PROD_WARP
+#define B200_PROD_WARP 0
+#endif
+#ifndef B200_MMA_WARP
+#define B200_MMA_WARP 1
+#endif
+#ifndef B200_PROD_POLL
+#define B200_PROD_POLL 1
+#endif
+#ifndef B200_MMA_POLL
+#define B200_MMA_POLL 1
+#endif
+#ifndef B200_EPI_POLL
+#define B200_EPI_POLL 0
+#endif
+#if B200_PROD_POLL
+#define B200_PROD_WAIT mbar_wait_poll<false, 64>
+#else
+#define B200_PROD_WAIT mbar_wait<false, 0>
+#endif
+#if B200_MMA_POLL
+#define B200_MMA_WAIT mbar_wait_poll<false, 20>
+#else
+#define B200_MMA_WAIT mbar_wait<false, 0>
+#endif
+#if B200_EPI_POLL
+#define B200_EPI_WAIT mbar_wait_poll<false, 20>
+#else
+#define B200_EPI_WAIT mbar_wait<false, 0>
+#endif
 #ifdef B200_TRACE
-__device__ long long g_trace[16384];
+// [cta][epilogue warp][phase < 128][4 slots], then the MMA issuer's [phase < 128][4 slots]
+__device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
 #define B200_TRACE_EPI(slot)                                                                     \
     do {                                                                                         \
-        if (pair_id == 0 && cta == 0 && warp == 4 && lane == 0 && phase < 1024) g_trace[phase * 4 + (slot)] = clock64(); \
+        if (pair_id == 0 && lane == 0 && phase < 128)                                            \
+            g_trace[((static_cast<int>(cta) * 8 + ew) * 128 + phase) * 8 + (slot)] = clock64();   \
     } while (0)
 #define B200_TRACE_MMA(slot)                                                                     \
     do {                                                                                         \
-        if (pair_id == 0 && phase < 1024) g_trace[8192 + phase * 4 + (slot)] = clock64();         \
+        if (pair_id == 0 && phase < 128) g_trace[2 * 8 * 128 * 8 + phase * 8 + (slot)] = clock64(); \
     } while (0)
 #else
 #define B200_TRACE_EPI(slot)
@@ -84,6 +141,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t bar_acce0 = bar_accf0 + 2 * 8;                       // used in the leader only
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // block-scale: ring of A-scale slots (128 fp32 each) filled by the producer, one barrier per slot
+    const uint32_t bar_sf0 = bar_acce0 + 2 * 8 + 8;
+    const uint32_t sfa_ring0 = bar_full0 + 1024;
+    const float* sfa_ring = reinterpret_cast<const float*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 1024);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -101,6 +162,8 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             mbar_init(bar_accf0 + s * 8, 1);          // one tcgen05.commit per use
             mbar_init(bar_acce0 + s * 8, 16);         // 8 epilogue warps in each of the two CTAs
         }
+        if constexpr (MODE == MODE_BLOCK)
+            for (int s = 0; s < Cfg::SFA_RING; ++s) mbar_init(bar_sf0 + s * 8, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -131,7 +194,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         // fall through to the teardown
     } else if (warp < 4) {
         setmaxnreg_dec<40>();
-        if (warp == 0 && lane == 0) {
+        if (warp == B200_PROD_WARP && lane == 0) {
             // ------------------------------ TMA producer (both CTAs) ------------------------------
             uint32_t it = 0;
             bool ok = true;
@@ -144,7 +207,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait<true>(bar_empty0 + s * 8, ph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_EMPTY)) {
+                    if (!B200_PROD_WAIT(bar_empty0 + s * 8, ph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_EMPTY)) {
                         ok = false;
                         break;
                     }
@@ -159,6 +222,16 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, b);
                     else
                         tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), b);
+                    if constexpr (MODE == MODE_BLOCK) {
+                        if (p.sfa_tma) {
+                            // this CTA's 128 A scales of K group kb -> slot it % (2*STAGES).  Twice as many slots
+                            // as stages: a slot is rewritten only after the MMAs of STAGES groups later have
+                            // started, long after the epilogue read it.
+                            const uint32_t slot = it % Cfg::SFA_RING;
+                            mbar_arrive_expect_tx(bar_sf0 + slot * 8, 512);
+                            tma_load_3d(sfa_ring0 + slot * 512, &p.tmap_sfa, bar_sf0 + slot * 8, row_a, kb, b);
+                        }
+                    }
                     if constexpr (MODE == MODE_MX) {
                         // scale atoms [batch][K/128][rows/128][512 B], addressed as rows of 256 bytes
                         const long long atom_a = b * (p.sfa_batch >> 9) + static_cast<long long>(kb) * p.sfa_stride + (mi * 2 + cta);
@@ -168,7 +241,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                 }
             }
-        } else if (warp == 1 && lane == 0 && cta == 0) {
+        } else if (warp == B200_MMA_WARP && lane == 0 && cta == 0) {
             // ------------------------------ UMMA issuer (leader only) ------------------------------
             uint32_t it = 0, phase = 0;
             bool ok = true;
@@ -177,20 +250,23 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 for (int g = 0; g < groups && ok; ++g, ++phase) {
                     const uint32_t as = phase % ACC_STAGES;
                     const uint32_t aph = (phase / ACC_STAGES) & 1;
-                    B200_TRACE_MMA(0);
-                    if (!mbar_wait<true>(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
-                        ok = false;
-                        break;
-                    }
-                    B200_TRACE_MMA(1);
-                    tc_fence_after();
                     const uint32_t tacc = tmem_base + as * BN;
                     for (int kb = 0; kb < kb_per_group; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait<true>(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
+                        // operands first (they were prefetched long ago), then the accumulator buffer: the
+                        // second wait is the latency-critical one and the MMAs follow it immediately
+                        if (!B200_MMA_WAIT(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
                             ok = false;
                             break;
+                        }
+                        if (kb == 0) {
+                            B200_TRACE_MMA(0);
+                            if (!B200_MMA_WAIT(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
+                                ok = false;
+                                break;
+                            }
+                            B200_TRACE_MMA(1);
                         }
                         B200_TRACE_MMA(2);
                         tc_fence_after();
@@ -206,6 +282,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         }
 #pragma unroll
                         for (int k = 0; k < BK / 32; ++k) {
+                            // Pacing: an MMA issued into a full tensor queue stalls at dispatch and takes the
+                            // whole scheduler (and the two epilogue warps on it) with it.  Two MMAs are queued at
+                            // once; the later ones are issued after a short sleep, when a slot is about to free.
+                            if (B200_PACE_NS > 0 && MODE == MODE_BLOCK && k >= 2) __nanosleep(B200_PACE_NS);
                             const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, kSwizzle128B);
                             uint64_t db;
                             if constexpr (Cfg::BLAYOUT == BL_NK) {
@@ -222,6 +302,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                 umma_f8<2>(tacc, da, db, idesc, accum);
                             }
                         }
+                        if (B200_PACE_NS > 0 && MODE == MODE_BLOCK) __nanosleep(B200_PACE_COMMIT_NS);
                         umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
                     }
                     if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs
@@ -269,63 +350,78 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 const bool col_ok = col_base < p.n;
                 const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
                 const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(blk0) * p.sfb_stride;
-                float sa_next = __ldg(sfa_p);
-                float sb0_next = col_ok ? __ldg(sfb_p) : 0.0f;
-                float sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
+                const bool sfa_tma = p.sfa_tma != 0;
+                float sa_cur = sfa_tma ? 0.0f : __ldg(sfa_p);
+                float sb0_cur = col_ok ? __ldg(sfb_p) : 0.0f;
+                float sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
                 for (int g = 0; g < groups; ++g, ++phase) {
-                    const float s0 = sa_next * sb0_next, s1 = kStraddle ? sa_next * sb1_next : s0;
-                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
-                    if (g + 1 < groups) {
-                        sa_next = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
-                        sb0_next = col_ok ? __ldg(sfb_p + g + 1) : 0.0f;
-                        if (kStraddle) sb1_next = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
+                    if (sfa_tma) {
+                        // staged by the producer; its barrier completed long before the MMAs of this group ran
+                        const uint32_t slot = phase % Cfg::SFA_RING;
+                        if (!mbar_wait<false, 0>(bar_sf0 + slot * 8, (phase / Cfg::SFA_RING) & 1, abort_flag, p.status,
+                                                 KSTAT_TIMEOUT_FULL)) {
+                            ok = false;
+                            break;
+                        }
+                        sa_cur = sfa_ring[slot * 128 + quad * 32 + lane];
                     }
+                    const float s0 = sa_cur * sb0_cur, s1 = kStraddle ? sa_cur * sb1_cur : s0;
+                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
                     const uint32_t as = phase & 1;
                     const uint32_t aph = (phase >> 1) & 1;
-                    if (!mbar_wait<true>(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
+                    if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
                         ok = false;
                         break;
                     }
+                    B200_TRACE_EPI(6);
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
                     B200_TRACE_EPI(0);
-                    // 32-column loads, one load ahead of the FMAs; a 16-column tail when NCH % 32 != 0.
-                    // The buffer goes back to the MMA issuer as soon as the last load has landed.
+                    // 32-column loads into two register buffers, both in flight at the start; a 16-column tail
+                    // when NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load
+                    // has landed, before the last FMAs; the next group's scales are fetched after that arrive
+                    // (an arrive waits for the thread's outstanding loads).
                     constexpr int C32 = NCH / 32, TAIL = NCH % 32;
+                    constexpr int NLD = C32 + (TAIL ? 1 : 0);            // loads per group
                     float v[2][32];
                     tmem_ld32(taddr, v[0]);
+                    if (NLD > 1) {
+                        if (C32 > 1) tmem_ld32(taddr + 32, v[1]);
+                        else tmem_ld16(taddr + 32, v[1]);
+                    }
 #pragma unroll
-                    for (int c = 0; c < C32; ++c) {
-                        tmem_ld_wait();
-                        if (c + 1 < C32) {
-                            tmem_ld32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
-                        } else if (TAIL) {
-                            tmem_ld16(taddr + C32 * 32, v[(c + 1) & 1]);
-                        } else {
+                    for (int c = 0; c < NLD; ++c) {
+                        tmem_ld_wait();                                  // every load issued so far (up to c+1) has landed
+                        if (c == 0) B200_TRACE_EPI(3);
+                        if (c == (NLD >= 2 ? NLD - 2 : 0)) {
+                            // the final load is among them: hand the TMEM buffer back, then fetch the next scales
+                            B200_TRACE_EPI(4);
                             tc_fence_before();
                             __syncwarp();
+                            B200_TRACE_EPI(5);
                             if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
                             B200_TRACE_EPI(1);
+                            if (g + 1 < groups) {
+                                if (!sfa_tma) sa_cur = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
+                                sb0_cur = col_ok ? __ldg(sfb_p + g + 1) : 0.0f;
+                                if (kStraddle) sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
+                            }
                         }
                         const unsigned long long scA = (!kStraddle || c * 32 < split) ? sc0 : sc1;
                         const unsigned long long scB = (!kStraddle || c * 32 + 16 < split) ? sc0 : sc1;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             acc[c * 16 + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), scA, acc[c * 16 + j]);
+                        if (c < C32) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
-                    }
-                    if (TAIL) {
-                        tmem_ld_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
-                        B200_TRACE_EPI(1);
-                        const unsigned long long scT = (!kStraddle || C32 * 32 < split) ? sc0 : sc1;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            acc[C32 * 16 + j] = ffma2(pack_f32x2(v[C32 & 1][2 * j], v[C32 & 1][2 * j + 1]), scT, acc[C32 * 16 + j]);
+                            for (int j = 0; j < 8; ++j)
+                                acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
+                        }
+                        // refill the buffer just consumed with chunk c+2
+                        if (c + 2 < NLD) {
+                            if (c + 2 < C32) tmem_ld32(taddr + (c + 2) * 32, v[c & 1]);
+                            else tmem_ld16(taddr + (c + 2) * 32, v[c & 1]);
+                        }
                     }
                     B200_TRACE_EPI(2);
                 }
@@ -335,8 +431,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         float o[16];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            o[2 * j] = __uint_as_float(static_cast<uint32_t>(acc[c * 8 + j]));
-                            o[2 * j + 1] = __uint_as_float(static_cast<uint32_t>(acc[c * 8 + j] >> 32));
+                            unpack_f32x2(acc[c * 8 + j], o[2 * j], o[2 * j + 1]);
                         }
                         store_row_chunk<16>(p, crow, col_base + c * 16, o, vec_ok);
                     }
@@ -344,7 +439,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             } else {
                 const uint32_t as = phase % ACC_STAGES;
                 const uint32_t aph = (phase / ACC_STAGES) & 1;
-                if (!mbar_wait<true>(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
+                if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
                     ok = false;
                     break;
                 }

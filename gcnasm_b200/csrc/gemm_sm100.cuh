@@ -27,8 +27,9 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1 };
 struct GemmParams {
     CUtensorMap tmap_a;          // u8 [batch][M][K], box 128 x 128, 128-byte swizzle
     CUtensorMap tmap_b;          // u8 [batch][N][K] (same box) or the flat 4-D view
-    CUtensorMap tmap_sfa;        // pair kernels, MX only: scale atoms as u8 [atoms*2][256], box 256 x 2
-    CUtensorMap tmap_sfb;        //                                                       box 256 x 2*atoms
+    CUtensorMap tmap_sfa;        // pair kernels.  MX: scale atoms as u8 [atoms*2][256], box 256 x 2.
+                                 //   block-scale: fp32 SFA [batch][K/128][M], box 128 x 1 (when sfa_tma != 0)
+    CUtensorMap tmap_sfb;        // pair kernels, MX: box 256 x 2*atoms
     void* c;
     const float* sfa;            // block: fp32 [K/128][M];   MX: E8M0 atoms (uint8, see sf_relayout)
     const float* sfb;            // block: fp32 [N/128][K/128]; MX: E8M0 atoms
@@ -39,6 +40,7 @@ struct GemmParams {
     int m, n, k, batch;
     int tiles_m, tiles_n, tiles_total, kblocks;
     int out_dtype;
+    int sfa_tma;                 // block-scale pair kernels: A scales are staged through shared memory by TMA
     int* status;
 };
 

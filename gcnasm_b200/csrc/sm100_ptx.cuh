@@ -61,9 +61,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// arrive on a barrier that lives in another CTA of the cluster (address from mapa)
+// Arrive on a barrier that may live in the partner CTA (address from mapa).  Default semantics on purpose:
+// a cluster-scope release here was measured at ~1200 clocks because it waits for every outstanding load of
+// the thread; the hand-offs it is used for are ordered by tcgen05.fence, not by generic-proxy memory.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -92,14 +94,50 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
 // Bounded wait.  `abort_flag` is a CTA-shared int; `status` the device status word.  The fast path is a
 // bare try_wait loop (each try_wait already suspends the thread for a hardware-defined interval); only a
 // wait that has failed many times starts reading the wall clock and checking the abort flag.
-template <bool kClusterScope = false>
+// kBackoffNs > 0 makes a waiting thread sleep between polls: the single-thread producer and MMA-issuer
+// roles use it so that their polling does not take issue slots from the epilogue warps that share their
+// scheduler.
+template <bool kClusterScope = false, int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (kBackoffNs > 0) __nanosleep(kBackoffNs);
         if ((++spins & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitBudgetNs) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Polling wait (mbarrier.test_wait never suspends the thread): for the latency-critical hand-offs between
+// the MMA issuer and the epilogue warps.  A suspended try_wait was observed to wake late when another
+// thread on the same scheduler is itself waiting on a different barrier.
+template <bool kClusterScope = false, int kBackoffNs = 0>
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        uint32_t ok;
+        if (kClusterScope)
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (kBackoffNs > 0) __nanosleep(kBackoffNs);
+        if ((++spins & 0x3FFFu) == 0) {
             if (*abort_flag) return false;
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
