@@ -193,7 +193,9 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
                 const int64_t rounds = (tiles + units - 1) / units;
                 // weight = relative time per output column: pairs with wide tiles feed the tensor pipe best,
                 // narrow and single-CTA tiles re-read more of A/B per flop from L2
-                const int64_t w = pair ? (bn >= 192 ? 10 : 13) : (bn >= 256 ? 14 : 18);
+                // (block-scale tiles that straddle the 128-column scale blocks pay for the second scale)
+                int64_t w = pair ? (bn >= 192 ? 10 : 13) : (bn >= 256 ? 14 : 18);
+                if (a->scale_mode == B200_SCALE_BLOCK && bn % 128 != 0) w += 2;
                 const int64_t cost = rounds * bn * w;
                 if (best < 0 || cost < best) {
                     best = cost;

@@ -50,7 +50,11 @@ struct DecodeCfg {
     static constexpr int STAGES_RAW = (225 * 1024 - 1024 - SF_SMEM) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SF_SMEM + 1024;
-    static constexpr int TMEM_COLS = 2 * MT < 32 ? 32 : 2 * MT;
+    // Block-scale mode gives every K group its own TMEM buffer out of a ring of NBUF: the hand-off between the
+    // MMA issuer and the epilogue warps costs on the order of a microsecond per group, far more than the tiny
+    // MMAs themselves, and only several groups in flight hide it under the weight stream.
+    static constexpr int NBUF = 4;
+    static constexpr int TMEM_COLS = NBUF * MT < 32 ? 32 : NBUF * MT;
     static constexpr int THREADS = 192;
     static constexpr int MAX_SF_FLOATS = SF_SMEM / 4;
     static_assert(MT == 16 || MT == 32 || MT == 64, "token block is 16, 32 or 64");
@@ -67,8 +71,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
     const uint32_t bar_full0 = smem_base + STAGES * Cfg::STAGE_BYTES;
     const uint32_t bar_empty0 = bar_full0 + STAGES * 8;
     const uint32_t bar_accf0 = bar_empty0 + STAGES * 8;
-    const uint32_t bar_acce0 = bar_accf0 + 2 * 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    constexpr int NBUF = Cfg::NBUF;
+    const uint32_t bar_acce0 = bar_accf0 + NBUF * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NBUF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* sf_smem = reinterpret_cast<float*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 1024);
 
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
             mbar_init(bar_full0 + s * 8, 1);
             mbar_init(bar_empty0 + s * 8, 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NBUF; ++s) {
             mbar_init(bar_accf0 + s * 8, 1);
             mbar_init(bar_acce0 + s * 8, 4);
         }
@@ -118,7 +123,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
                 const int kb = kb0 + i;
                 const uint32_t s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
-                if (!mbar_wait(bar_empty0 + s * 8, ph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_EMPTY)) break;
+                if (!mbar_wait_poll<false, 64>(bar_empty0 + s * 8, ph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_EMPTY)) break;
                 const uint32_t sw = smem_base + s * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
                 const uint32_t full = bar_full0 + s * 8;
@@ -143,17 +148,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
                 const uint32_t s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 uint32_t as = 0;
+                if (!mbar_wait_poll<false, 20>(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
+                    ok = false;
+                    break;
+                }
                 if constexpr (MODE == MODE_BLOCK) {
-                    as = phase & 1;
-                    const uint32_t aph = (phase >> 1) & 1;
-                    if (!mbar_wait(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
+                    as = phase % NBUF;
+                    const uint32_t aph = (phase / NBUF) & 1;
+                    if (!mbar_wait_poll<false, 20>(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
                         ok = false;
                         break;
                     }
-                }
-                if (!mbar_wait(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
-                    ok = false;
-                    break;
                 }
                 tc_fence_after();
                 const uint32_t sw = smem_base + s * Cfg::STAGE_BYTES;
@@ -205,8 +210,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
 
             uint32_t phase = 0;
             for (int i = 0; i < nkb; ++i, ++phase) {
-                const uint32_t as = phase & 1;
-                const uint32_t aph = (phase >> 1) & 1;
+                const uint32_t as = phase % NBUF;
+                const uint32_t aph = (phase / NBUF) & 1;
                 if (!mbar_wait(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
                     ok = false;
                     break;

@@ -28,11 +28,15 @@ struct PairCfg {
     static constexpr int SFA_BYTES = (MODE == MODE_MX) ? 512 : 0;
     static constexpr int SFB_BYTES = (MODE == MODE_MX) ? SFB_ATOMS * 512 : 0;
     static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
-    static constexpr int STAGES_RAW = (225 * 1024 - 1024) / STAGE_BYTES;
+    // 227 KB per CTA: ring stages (+ two 512-byte A-scale slots per stage in block-scale mode), 1 KB of
+    // barriers, 1 KB of alignment slack
+    static constexpr int PER_STAGE = STAGE_BYTES + ((MODE == MODE_BLOCK) ? 1024 : 0);
+    static constexpr int STAGES_RAW = (227 * 1024 - 2048) / PER_STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SFA_RING = 2 * STAGES;                     // block-scale: slots of 128 fp32 A scales
     static constexpr int SFA_RING_BYTES = (MODE == MODE_BLOCK) ? SFA_RING * 512 : 0;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + 1024;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
     static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
     static constexpr int ACC_COLS = ACC_STAGES * BN;
@@ -55,59 +59,23 @@ __device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, fl
 }
 // d = a * b + c on two packed fp32 lanes
 __device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-#ifdef B200_SCALAR_FMA
-    float a0, a1, b0, b1, c0, c1;
-    unpack_f32x2(a, a0, a1);
-    unpack_f32x2(b, b0, b1);
-    unpack_f32x2(c, c0, c1);
-    return pack_f32x2(fmaf(a0, b0, c0), fmaf(a1, b1, c1));
-#else
     unsigned long long d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
-#endif
 }
 
-// Wait flavours per role (see mbar_wait / mbar_wait_poll): 1 = poll with a short sleep, 0 = suspending try_wait.
-// All waits use the default (CTA-scope) acquire even when the arrivals come from the partner CTA: a
-// cluster-scope acquire was measured at ~430 clocks per wait, and every hand-off here is ordered through the
-// async proxy (TMA complete_tx, tcgen05.commit) or tcgen05.fence, not through generic-proxy memory.
-#ifndef B200_PACE_NS
-#define B200_PACE_NS 0
-#endif
-#ifndef B200_PACE_COMMIT_NS
-#define B200_PACE_COMMIT_NS 80
-#endif
-#ifndef B200_PROD_WARP
-#define B200_PROD_WARP 0
-#endif
-#ifndef B200_MMA_WARP
-#define B200_MMA_WARP 1
-#endif
-#ifndef B200_PROD_POLL
-#define B200_PROD_POLL 1
-#endif
-#ifndef B200_MMA_POLL
-#define B200_MMA_POLL 1
-#endif
-#ifndef B200_EPI_POLL
-#define B200_EPI_POLL 0
-#endif
-#if B200_PROD_POLL
+// Waits.  The single-thread roles poll (mbarrier.test_wait plus a short sleep), the epilogue warps use the
+// suspending try_wait.  Every wait uses the default CTA-scope acquire even when the arrivals come from the
+// partner CTA: a cluster-scope acquire was measured at ~430 clocks per wait, and each hand-off here is ordered
+// through the async proxy (TMA complete_tx, tcgen05.commit) or tcgen05.fence, not through generic memory.
 #define B200_PROD_WAIT mbar_wait_poll<false, 64>
-#else
-#define B200_PROD_WAIT mbar_wait<false, 0>
-#endif
-#if B200_MMA_POLL
 #define B200_MMA_WAIT mbar_wait_poll<false, 20>
-#else
-#define B200_MMA_WAIT mbar_wait<false, 0>
-#endif
-#if B200_EPI_POLL
-#define B200_EPI_WAIT mbar_wait_poll<false, 20>
-#else
 #define B200_EPI_WAIT mbar_wait<false, 0>
-#endif
+// UMMA issuer threads in block-scale mode (warps 1..kBlockIssuers of the leader CTA); at most the number of
+// TMEM buffers, because an issuer has to observe every phase of the barriers it waits on.
+static constexpr int kBlockIssuers = 2;
+// Building with -DB200_TRACE records clock64() stamps of the hand-offs of the first CTA pair into g_trace
+// (read back with b200_trace_read); it is how the latencies quoted in the comments here were measured.
 #ifdef B200_TRACE
 // [cta][epilogue warp][phase < 128][4 slots], then the MMA issuer's [phase < 128][4 slots]
 __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
@@ -194,7 +162,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         // fall through to the teardown
     } else if (warp < 4) {
         setmaxnreg_dec<40>();
-        if (warp == B200_PROD_WARP && lane == 0) {
+        if (warp == 0 && lane == 0) {
             // ------------------------------ TMA producer (both CTAs) ------------------------------
             uint32_t it = 0;
             bool ok = true;
@@ -241,13 +209,24 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                 }
             }
-        } else if (warp == B200_MMA_WARP && lane == 0 && cta == 0) {
+        } else if (warp >= 1 && warp <= ((MODE == MODE_BLOCK) ? kBlockIssuers : 1) && lane == 0 && cta == 0) {
             // ------------------------------ UMMA issuer (leader only) ------------------------------
+            // Block-scale mode runs several issuer threads (warps 1..kBlockIssuers, one per scheduler) that take the
+            // K groups round-robin.  An issuer is effectively tied up until its own MMAs and commits have gone
+            // through the tensor queue, so a single issuer cannot start group g+1 while group g executes; with
+            // several, the next group is already queued.  Order on a TMEM buffer is kept by its drained-buffer
+            // barrier, order on a ring stage by its full barrier.
+            constexpr uint32_t kIssuers = (MODE == MODE_BLOCK) ? kBlockIssuers : 1;
+            const uint32_t my_slot = static_cast<uint32_t>(warp - 1);
             uint32_t it = 0, phase = 0;
             bool ok = true;
             constexpr uint32_t idesc = make_idesc_f8(2 * BM, BN);
             for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
                 for (int g = 0; g < groups && ok; ++g, ++phase) {
+                    if (kIssuers > 1 && (phase % kIssuers) != my_slot) {
+                        it += kb_per_group;           // another issuer's group
+                        continue;
+                    }
                     const uint32_t as = phase % ACC_STAGES;
                     const uint32_t aph = (phase / ACC_STAGES) & 1;
                     const uint32_t tacc = tmem_base + as * BN;
@@ -282,10 +261,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         }
 #pragma unroll
                         for (int k = 0; k < BK / 32; ++k) {
-                            // Pacing: an MMA issued into a full tensor queue stalls at dispatch and takes the
-                            // whole scheduler (and the two epilogue warps on it) with it.  Two MMAs are queued at
-                            // once; the later ones are issued after a short sleep, when a slot is about to free.
-                            if (B200_PACE_NS > 0 && MODE == MODE_BLOCK && k >= 2) __nanosleep(B200_PACE_NS);
                             const uint64_t da = make_smem_desc(sa + k * 32, 16, 1024, kSwizzle128B);
                             uint64_t db;
                             if constexpr (Cfg::BLAYOUT == BL_NK) {
@@ -302,7 +277,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                 umma_f8<2>(tacc, da, db, idesc, accum);
                             }
                         }
-                        if (B200_PACE_NS > 0 && MODE == MODE_BLOCK) __nanosleep(B200_PACE_COMMIT_NS);
                         umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
                     }
                     if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs

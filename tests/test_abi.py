@@ -91,6 +91,8 @@ def test_validation_codes(native):
     assert chk(_args(**{**bs, "m": 64, "stride_sfa": 64})) == L.OK and tile.value == L.TILE_DECODE
     assert chk(_args(m=65)) == L.OK and tile.value != L.TILE_DECODE
     assert chk(_args(m=4096, n=7168, k=2048, stride_a=2048, stride_b=2048, stride_c=7168)) == L.OK and tile.value == L.TILE_PAIR_256x224
+    bs2 = dict(scale_mode=L.SCALE_BLOCK, ptr_sfa=0x4000, ptr_sfb=0x5000, stride_sfa=4096, stride_sfb=16)
+    assert chk(_args(m=4096, n=7168, k=2048, stride_a=2048, stride_b=2048, stride_c=7168, **bs2)) == L.OK and tile.value == L.TILE_PAIR_256x256
     assert chk(_args(m=8192, n=8192, k=8192, stride_a=8192, stride_b=8192, stride_c=8192)) == L.OK and tile.value == L.TILE_PAIR_256x256
     assert chk(_args(m=128, tile_hint=L.TILE_DECODE)) == L.ERR_UNSUPPORTED
     mx = dict(scale_mode=L.SCALE_MX, ptr_sfa=0x4000, ptr_sfb=0x5000)
