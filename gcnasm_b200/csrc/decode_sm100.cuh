@@ -50,11 +50,13 @@ struct DecodeCfg {
     static constexpr int STAGES_RAW = (225 * 1024 - 1024 - SF_SMEM) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SF_SMEM + 1024;
-    // Block-scale mode gives every K group its own TMEM buffer out of a ring of NBUF: the hand-off between the
-    // MMA issuer and the epilogue warps costs on the order of a microsecond per group, far more than the tiny
-    // MMAs themselves, and only several groups in flight hide it under the weight stream.
-    static constexpr int NBUF = 4;
-    static constexpr int TMEM_COLS = NBUF * MT < 32 ? 32 : NBUF * MT;
+    // Block-scale mode gives every K group its own TMEM buffer (a fresh accumulator per group), but hands the
+    // buffers over in BATCHES of GB groups: one hand-off between the MMA issuer and the epilogue warps costs on
+    // the order of a microsecond (commit -> barrier -> TMEM loads -> barrier), far more than the tiny MMAs of a
+    // group, so it is paid once per GB groups.  Two batch sets ping-pong: TMEM holds 2 x GB x MT columns.
+    static constexpr int GB = 4;
+    static constexpr int NBUF = 2;
+    static constexpr int TMEM_COLS = NBUF * GB * MT < 32 ? 32 : NBUF * GB * MT;
     static constexpr int THREADS = 192;
     static constexpr int MAX_SF_FLOATS = SF_SMEM / 4;
     static_assert(MT == 16 || MT == 32 || MT == 64, "token block is 16, 32 or 64");
@@ -144,45 +146,49 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
             if constexpr (MODE != MODE_BLOCK) {
                 // the single accumulator buffer is free at kernel start
             }
-            for (int i = 0; i < nkb && ok; ++i) {
-                const uint32_t s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                uint32_t as = 0;
-                if (!mbar_wait_poll<false, 20>(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
-                    ok = false;
-                    break;
-                }
+            constexpr int GBATCH = (MODE == MODE_BLOCK) ? Cfg::GB : 1;
+            for (int i0 = 0; i0 < nkb && ok; i0 += GBATCH, ++phase) {
+                const int gb = (nkb - i0 < GBATCH) ? nkb - i0 : GBATCH;       // groups in this batch
+                const uint32_t set = phase % NBUF;
                 if constexpr (MODE == MODE_BLOCK) {
-                    as = phase % NBUF;
                     const uint32_t aph = (phase / NBUF) & 1;
-                    if (!mbar_wait_poll<false, 20>(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
+                    if (!mbar_wait_poll<false, 20>(bar_acce0 + set * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
                         ok = false;
                         break;
                     }
                 }
-                tc_fence_after();
-                const uint32_t sw = smem_base + s * Cfg::STAGE_BYTES;
-                const uint32_t sx = sw + Cfg::W_BYTES;
-                const uint32_t tacc = tmem_base + as * MT;
-#pragma unroll
-                for (int k = 0; k < BK / 32; ++k) {
-                    uint64_t dw;
-                    if constexpr (Cfg::BLAYOUT == BL_NK) {
-                        dw = make_smem_desc(sw + k * 32, 16, 1024, kSwizzle128B);
-                    } else {
-                        constexpr uint32_t LBO = (BNW / 16) * 256;
-                        dw = make_smem_desc(sw + k * 2 * LBO, LBO, 128, kSwizzleNone);
+                for (int j = 0; j < gb && ok; ++j) {
+                    const int i = i0 + j;
+                    const uint32_t s = i % STAGES;
+                    const uint32_t ph = (i / STAGES) & 1;
+                    if (!mbar_wait_poll<false, 20>(bar_full0 + s * 8, ph, abort_flag, p.status, KSTAT_TIMEOUT_FULL)) {
+                        ok = false;
+                        break;
                     }
-                    const uint64_t dx = make_smem_desc(sx + k * 32, 16, 1024, kSwizzle128B);
-                    const uint32_t accum = (MODE == MODE_BLOCK) ? (k > 0 ? 1u : 0u) : ((i > 0 || k > 0) ? 1u : 0u);
-                    umma_f8<1>(tacc, dw, dx, idesc, accum);
+                    tc_fence_after();
+                    const uint32_t sw = smem_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t sx = sw + Cfg::W_BYTES;
+                    const uint32_t tacc = (MODE == MODE_BLOCK) ? tmem_base + (set * Cfg::GB + j) * MT : tmem_base;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k) {
+                        uint64_t dw;
+                        if constexpr (Cfg::BLAYOUT == BL_NK) {
+                            dw = make_smem_desc(sw + k * 32, 16, 1024, kSwizzle128B);
+                        } else {
+                            constexpr uint32_t LBO = (BNW / 16) * 256;
+                            dw = make_smem_desc(sw + k * 2 * LBO, LBO, 128, kSwizzleNone);
+                        }
+                        const uint64_t dx = make_smem_desc(sx + k * 32, 16, 1024, kSwizzle128B);
+                        const uint32_t accum = (MODE == MODE_BLOCK) ? (k > 0 ? 1u : 0u) : ((i > 0 || k > 0) ? 1u : 0u);
+                        umma_f8<1>(tacc, dw, dx, idesc, accum);
+                    }
+                    umma_commit<1>(bar_empty0 + s * 8);
                 }
-                umma_commit<1>(bar_empty0 + s * 8);
+                if (!ok) break;
                 if constexpr (MODE == MODE_BLOCK) {
-                    umma_commit<1>(bar_accf0 + as * 8);
-                    ++phase;
+                    umma_commit<1>(bar_accf0 + set * 8);
                 } else {
-                    if (i == nkb - 1) umma_commit<1>(bar_accf0);
+                    if (i0 + gb >= nkb) umma_commit<1>(bar_accf0);
                 }
             }
         }
@@ -209,30 +215,38 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
             asm volatile("bar.sync 1, 128;" ::: "memory");   // epilogue warps only
 
             uint32_t phase = 0;
-            for (int i = 0; i < nkb; ++i, ++phase) {
-                const uint32_t as = phase % NBUF;
+            for (int i0 = 0; i0 < nkb && ok; i0 += Cfg::GB, ++phase) {
+                const int gb = (nkb - i0 < Cfg::GB) ? nkb - i0 : Cfg::GB;
+                const uint32_t set = phase % NBUF;
                 const uint32_t aph = (phase / NBUF) & 1;
-                if (!mbar_wait(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
+                if (!mbar_wait(bar_accf0 + set * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                float v[MT];
+                for (int j = 0; j < gb; ++j) {
+                    const int i = i0 + j;
+                    float v[MT];
 #pragma unroll
-                for (int c = 0; c < MT / 16; ++c) tmem_ld16(tmem_base + tmem_lane + as * MT + c * 16, &v[c * 16]);
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_acce0 + as * 8);
-                const float sb = sf_smem[nkb * MT + i];
-                const float4* sa4 = reinterpret_cast<const float4*>(sf_smem + i * MT);
+                    for (int c = 0; c < MT / 16; ++c)
+                        tmem_ld16(tmem_base + tmem_lane + (set * Cfg::GB + j) * MT + c * 16, &v[c * 16]);
+                    tmem_ld_wait();
+                    if (j == gb - 1) {
+                        // the whole batch is in registers: the set goes back to the MMA issuer
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_acce0 + set * 8);
+                    }
+                    const float sb = sf_smem[nkb * MT + i];
+                    const float4* sa4 = reinterpret_cast<const float4*>(sf_smem + i * MT);
 #pragma unroll
-                for (int j = 0; j < MT; j += 4) {
-                    const float4 sa = sa4[j / 4];
-                    acc[j + 0] = fmaf(v[j + 0], sa.x * sb, acc[j + 0]);
-                    acc[j + 1] = fmaf(v[j + 1], sa.y * sb, acc[j + 1]);
-                    acc[j + 2] = fmaf(v[j + 2], sa.z * sb, acc[j + 2]);
-                    acc[j + 3] = fmaf(v[j + 3], sa.w * sb, acc[j + 3]);
+                    for (int jj = 0; jj < MT; jj += 4) {
+                        const float4 sa = sa4[jj / 4];
+                        acc[jj + 0] = fmaf(v[jj + 0], sa.x * sb, acc[jj + 0]);
+                        acc[jj + 1] = fmaf(v[jj + 1], sa.y * sb, acc[jj + 1]);
+                        acc[jj + 2] = fmaf(v[jj + 2], sa.z * sb, acc[jj + 2]);
+                        acc[jj + 3] = fmaf(v[jj + 3], sa.w * sb, acc[jj + 3]);
+                    }
                 }
             }
         } else {
