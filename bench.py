@@ -37,6 +37,9 @@ WORKLOADS = {
     "cube8192": (8192, 8192, 8192),
 }
 SEED = 1234
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
+# summarised in profiles/ (None where no capture of that workload exists)
+NCU_TRAFFIC_BYTES = {"c2": None}
 
 
 def measured_peaks():
@@ -286,7 +289,7 @@ def main():
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     achieved = 2.0 * m * n * k / (launch_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                "traffic": None, "kernel": "gemm_a8w8_sm100_kernel<BN=256, block-scale>",
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel": "gemm_a8w8_pair_sm100_kernel<256x256 pair tile, block-scale>",
                 "peak_source": f"2 x bf16 cuBLAS burst ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}); fp8 issues at twice the bf16 rate",
                 "frac_of_nominal_4500": achieved / 4500.0}
 
