@@ -31,11 +31,12 @@ struct PairCfg {
     // 227 KB per CTA: ring stages (+ two 512-byte A-scale slots per stage in block-scale mode), 1 KB of
     // barriers, 1 KB of alignment slack
     static constexpr int PER_STAGE = STAGE_BYTES + ((MODE == MODE_BLOCK) ? 1024 : 0);
-    static constexpr int STAGES_RAW = (227 * 1024 - 2048) / PER_STAGE;
+    static constexpr int OUT_STAGE_BYTES = 8 * kOutStageBytesPerWarp;   // epilogue store staging, one buffer per warp
+    static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES) / PER_STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SFA_RING = 2 * STAGES;                     // block-scale: slots of 128 fp32 A scales
     static constexpr int SFA_RING_BYTES = (MODE == MODE_BLOCK) ? SFA_RING * 512 : 0;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + OUT_STAGE_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
     static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
@@ -296,6 +297,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && ((p.ldc * esz) % 16 == 0) &&
                             ((p.c_batch * esz) % 16 == 0);
         const uint32_t leader_acce0 = mapa_shared(bar_acce0, 0);
+        uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 + Cfg::SFA_RING_BYTES + ew * kOutStageBytesPerWarp;
         float tscale = 1.0f;
         if constexpr (MODE == MODE_ACC) {
             if (p.scale_a) tscale *= __ldg(p.scale_a);
@@ -307,9 +309,9 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             int b, mi, ni;
             tile_coords(p, t, b, mi, ni);
             const int row = mi * (2 * BM) + row_in_tile;
+            const int row0 = row - lane;                       // output row of this warp's lane 0
             const int col_base = ni * BN + half * NCH;
-            uint8_t* crow = reinterpret_cast<uint8_t*>(p.c) +
-                            (static_cast<size_t>(b) * p.c_batch + static_cast<size_t>(row) * p.ldc) * esz;
+            uint8_t* cbatch = reinterpret_cast<uint8_t*>(p.c) + static_cast<size_t>(b) * p.c_batch * esz;
 
             if constexpr (MODE == MODE_BLOCK) {
                 unsigned long long acc[NCH / 2];
@@ -399,15 +401,31 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     B200_TRACE_EPI(2);
                 }
-                if (ok && row < p.m) {
+                if (ok) {
+                    // 64-byte row segments: 32 columns of bf16 or 16 columns of fp32 per pass
+                    if (p.out_dtype == OUT_BF16) {
 #pragma unroll
-                    for (int c = 0; c < NCH / 16; ++c) {
-                        float o[16];
+                        for (int c = 0; c + 1 < NCH / 16; c += 2) {
+                            float o[32];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            unpack_f32x2(acc[c * 8 + j], o[2 * j], o[2 * j + 1]);
+                            for (int j = 0; j < 16; ++j) unpack_f32x2(acc[c * 8 + j], o[2 * j], o[2 * j + 1]);
+                            store_chunk_coalesced<32>(p, cbatch, out_stage, row0, col_base + c * 16, o, lane, vec_ok);
                         }
-                        store_row_chunk<16>(p, crow, col_base + c * 16, o, vec_ok);
+                        if ((NCH / 16) & 1) {
+                            constexpr int c = NCH / 16 - 1;
+                            float o[16];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) unpack_f32x2(acc[c * 8 + j], o[2 * j], o[2 * j + 1]);
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * 16, o, lane, vec_ok);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < NCH / 16; ++c) {
+                            float o[16];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) unpack_f32x2(acc[c * 8 + j], o[2 * j], o[2 * j + 1]);
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * 16, o, lane, vec_ok);
+                        }
                     }
                 }
             } else {
@@ -436,7 +454,12 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                         for (int j = 0; j < CW; ++j) v[c & 1][j] *= tscale;
                     }
-                    if (row < p.m) store_row_chunk<CW>(p, crow, col_base + c * CW, v[c & 1], vec_ok);
+                    if (p.out_dtype == OUT_BF16 || CW == 16) {
+                        store_chunk_coalesced<CW>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
+                    } else {
+                        store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
+                        store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW + 16, v[c & 1] + 16, lane, vec_ok);
+                    }
                 }
                 ++phase;
             }

@@ -119,6 +119,56 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, void* crow,
     }
 }
 
+// Coalesced store of one warp's 32-row x CNT-column chunk.  Every lane holds CNT consecutive columns of ITS row
+// (the TMEM load layout), so a direct store would touch 32 different rows per instruction.  The chunk is written
+// to a warp-private shared-memory buffer (row pitch 80 B: 16-byte accesses stay conflict-free) and read back
+// transposed, so that one store instruction covers whole 32- or 64-byte row segments.
+// `row0` is the output row of lane 0; `stage` is this warp's 2560-byte buffer; CNT * element size is 32 or 64.
+static constexpr int kOutStagePitch = 80;
+static constexpr int kOutStageBytesPerWarp = 32 * kOutStagePitch;
+template <int CNT>
+__device__ __forceinline__ void store_chunk_coalesced(const GemmParams& p, uint8_t* cbatch, uint8_t* stage, int row0,
+                                                      int col0, const float* v, int lane, bool vec_ok) {
+    const bool bf16 = p.out_dtype == OUT_BF16;
+    const int esz = bf16 ? 2 : 4;
+    if (!(vec_ok && col0 + CNT <= p.n)) {
+        // ragged edge or unaligned output: per-lane path
+        const int row = row0 + lane;
+        if (row < p.m) store_row_chunk<CNT>(p, cbatch + static_cast<size_t>(row) * p.ldc * esz, col0, v, false);
+        return;
+    }
+    uint8_t* mine = stage + lane * kOutStagePitch;
+    int row_bytes;
+    if (bf16) {
+        row_bytes = CNT * 2;
+#pragma unroll
+        for (int j = 0; j < CNT; j += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(v[j + 0], v[j + 1]);
+            w.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            w.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            w.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(mine + j * 2) = w;
+        }
+    } else {
+        row_bytes = CNT * 4;
+#pragma unroll
+        for (int j = 0; j < CNT; j += 4)
+            *reinterpret_cast<float4*>(mine + j * 4) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+    __syncwarp();
+    const int chunks = row_bytes >> 4;                  // 16-byte pieces per row: 2, 4 or 8
+    const int rows_per_pass = 32 / chunks;
+    const int c = lane % chunks, r_in = lane / chunks;
+    for (int r = r_in; r < 32; r += rows_per_pass) {
+        const uint4 w = *reinterpret_cast<const uint4*>(stage + r * kOutStagePitch + c * 16);
+        const int row = row0 + r;
+        if (row < p.m)
+            *reinterpret_cast<uint4*>(cbatch + (static_cast<size_t>(row) * p.ldc + col0) * esz + c * 16) = w;
+    }
+    __syncwarp();
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_a8w8_sm100_kernel(const __grid_constant__ GemmParams p) {
     constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES, MODE = Cfg::MODE;

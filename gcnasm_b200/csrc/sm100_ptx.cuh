@@ -65,7 +65,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // a cluster-scope release here was measured at ~1200 clocks because it waits for every outstanding load of
 // the thread; the hand-offs it is used for are ordered by tcgen05.fence, not by generic-proxy memory.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+#ifdef B200_RELAXED_ARRIVE
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#else
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#endif
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
