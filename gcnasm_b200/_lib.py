@@ -22,7 +22,7 @@ OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, E
 
 # every symbol include/b200gemm.h declares
 EXPORTS = (
-    "b200_gemm_a8w8", "b200_gemm_check", "b200_gemm_a8w8_simple", "b200_gemm_a8w8_host",
+    "b200_gemm_a8w8", "b200_gemm_check", "b200_gemm_a8w8_simple", "b200_gemm_a8w8_host", "b200_gemm_a8w8_decode_static",
     "b200_shuffle_b", "b200_unshuffle_b",
     "b200_cast_e4m3", "b200_quantize_tensor", "b200_quantize_tensor_workspace", "b200_quantize_1x128",
     "b200_quantize_128x128", "b200_quantize_mx32", "b200_mx_sf_relayout", "b200_mx_sf_bytes",
@@ -77,6 +77,7 @@ def lib() -> C.CDLL:
         "b200_gemm_check": (i32, [P, C.POINTER(i32)]),
         "b200_gemm_a8w8_simple": (i32, [P, vp]),
         "b200_gemm_a8w8_host": (i32, [P, vp]),
+        "b200_gemm_a8w8_decode_static": (i32, [P, vp]),
         "b200_shuffle_b": (i32, [vp, vp, i64, i64, i32, vp]),
         "b200_unshuffle_b": (i32, [vp, vp, i64, i64, i32, vp]),
         "b200_cast_e4m3": (i32, [vp, vp, i64, vp]),

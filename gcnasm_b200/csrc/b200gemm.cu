@@ -407,6 +407,85 @@ int run_decode(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStr
     return B200_OK;
 }
 
+// ---- allocation-free decode variant -------------------------------------------------------------------
+// Split-K scratch that lives in the library image instead of in cudaMalloc'd memory: every GPU that loads the
+// library holds these bytes until the process exits.  In host code the NAME of the array is only a host-side
+// handle, not a device address; the address each device uses comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+constexpr size_t kStaticScratchFloats = 256 * 1024;                   // 1 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+int run_decode_static(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return B200_ERR_NO_DEVICE;
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_static_scratch_ptr[dev]) {
+            void* sym = nullptr;
+            CU_TRY(cudaGetSymbolAddress(&sym, g_static_scratch));     // this device's copy of the array
+            g_static_scratch_ptr[dev] = static_cast<float*>(sym);
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    const size_t need = pl.splits > 1 ? static_cast<size_t>(pl.splits) * a->batch * a->m * a->n : 0;
+    if (need > kStaticScratchFloats) return B200_ERR_TOO_LARGE;
+
+    DecodeParams p;
+    std::memset(&p, 0, sizeof(p));
+    int rc;
+    if (a->b_layout == B200_B_NK_ROWMAJOR)
+        rc = make_rowmajor_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, 128);
+    else
+        rc = make_flat_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, 128);
+    if (rc) return rc;
+    rc = make_rowmajor_tmap(&p.tmap_x, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, pl.mt);
+    if (rc) return rc;
+    p.c = a->ptr_c;
+    p.sfa = static_cast<const float*>(a->ptr_sfa);
+    p.sfb = static_cast<const float*>(a->ptr_sfb);
+    p.scale_a = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_a : nullptr;
+    p.scale_b = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_b : nullptr;
+    p.ldc = a->stride_c;
+    p.c_batch = a->stride_c_batch;
+    p.sfa_stride = a->stride_sfa;
+    p.sfb_stride = a->stride_sfb;
+    p.sfa_batch = a->stride_sfa_batch;
+    p.sfb_batch = a->stride_sfb_batch;
+    p.m = static_cast<int>(a->m);
+    p.n = static_cast<int>(a->n);
+    p.k = static_cast<int>(a->k);
+    p.batch = static_cast<int>(a->batch);
+    p.tiles_n = static_cast<int>((a->n + 127) / 128);
+    p.kblocks = static_cast<int>((a->k + 127) / 128);
+    p.splits = pl.splits;
+    p.kb_per_split = (p.kblocks + pl.splits - 1) / pl.splits;
+    p.out_dtype = a->out_dtype;
+    p.status = ds->status_ptr;
+    // every element of the partials that the reduction reads is written by this launch first, so nothing in
+    // the shared array has to be cleared between calls
+    p.partial = pl.splits > 1 ? scratch : nullptr;
+    const int grid = p.tiles_n * p.batch * pl.splits;
+    const bool block = a->scale_mode == B200_SCALE_BLOCK;
+    if (a->b_layout == B200_B_NK_ROWMAJOR)
+        rc = block ? launch_decode_mt<MODE_BLOCK, BL_NK>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_NK>(pl.mt, p, grid, st);
+    else
+        rc = block ? launch_decode_mt<MODE_BLOCK, BL_FLAT>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_FLAT>(pl.mt, p, grid, st);
+    if (rc) return rc;
+    if (pl.splits > 1) {
+        const long long per_split = static_cast<long long>(a->batch) * a->m * a->n;
+        const int threads = 256;
+        const unsigned blocks = static_cast<unsigned>((per_split + threads - 1) / threads);
+        decode_splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.partial, a->ptr_c, pl.splits, per_split, p.m, p.n,
+                                                               p.ldc, p.c_batch, p.out_dtype);
+        CU_TRY(cudaGetLastError());
+        g_launches.fetch_add(1);
+    }
+    return B200_OK;
+}
+
 int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
     int BN = 128;
     bool pair = false;
@@ -550,6 +629,19 @@ int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream) {
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     if (pl.tile == B200_TILE_DECODE) return run_decode(args, pl, ds, st);
     return run_gemm(args, pl, ds, st);
+}
+
+int b200_gemm_a8w8_decode_static(const b200_gemm_args* args, void* cuda_stream) {
+    Plan pl;
+    int rc = validate(args, 148, &pl);
+    if (rc) return rc;
+    DeviceState* ds = nullptr;
+    rc = device_state(&ds);
+    if (rc) return rc;
+    rc = validate(args, ds->sm_count, &pl);
+    if (rc) return rc;
+    if (pl.tile != B200_TILE_DECODE) return B200_ERR_UNSUPPORTED;      // only the skinny-M kernel has this variant
+    return run_decode_static(args, pl, ds, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int b200_gemm_a8w8_simple(const b200_gemm_args* a, void* cuda_stream) {

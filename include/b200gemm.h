@@ -93,6 +93,24 @@ int b200_gemm_a8w8_simple(const b200_gemm_args* args, void* cuda_stream);
  * Device buffers are cached per device and grown on demand; b200_release() frees them.                  */
 int b200_gemm_a8w8_host(const b200_gemm_args* host_args, void* cuda_stream);
 
+/* No counterpart in the reference.  Skinny-M (M <= 64) GEMM with the same arguments and the same results as
+ * b200_gemm_a8w8, for callers that must not allocate device memory while they run: code inside a serving
+ * loop whose memory was carved up ahead of time, a real-time or latency-critical thread where cudaMalloc's
+ * device-wide synchronisation is unacceptable, or a host that hands this library a fixed memory budget and
+ * forbids it to grow.  b200_gemm_a8w8 may cudaMalloc (and later cudaFree) a split-K workspace when a skinny
+ * problem has fewer 128-row weight panels than the GPU has SMs; this entry point never calls cudaMalloc,
+ * cudaFree or any allocating routine.  Its split-K workspace is a fixed 1 MiB array inside the library image
+ * (every GPU that loads the library holds it until the process exits).
+ *   - Limit: splits * batch * M * N fp32 partials must fit in 1 MiB (262,144 floats); otherwise the call
+ *     returns B200_ERR_TOO_LARGE and launches nothing.  Shapes the launcher would not send to the skinny-M
+ *     kernel (M > 64, MX scales) return B200_ERR_UNSUPPORTED.
+ *   - The first call on each device looks up that device's address of the array (and the library's other
+ *     per-device set-up); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing needs
+ *     clearing (each launch writes every partial it later reads), but two calls that overlap on the GPU --
+ *     different streams, or the same stream from different threads without ordering -- race on it.            */
+int b200_gemm_a8w8_decode_static(const b200_gemm_args* args, void* cuda_stream);
+
 /* ---- weight pre-shuffle -------------------------------------------------------------------- */
 /* shuffle_b (flatmm_a8w8_gfx950.cc:638-681) on the device: src is [K][N] row-major when src_is_kn != 0
  * (the reference's input) or [N][K] row-major otherwise; dst is [N/16][K/16][16][16].  Bit-exact byte
