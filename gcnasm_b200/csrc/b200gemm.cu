@@ -528,6 +528,16 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 3, d, st, bx, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32))) return rc;
         p.sfa_tma = 1;
     }
+    if (pair && a->scale_mode == B200_SCALE_BLOCK && a->out_dtype == B200_OUT_BF16 && aligned16(a->ptr_c) &&
+        a->stride_c % 8 == 0 && (a->batch == 1 || a->stride_c_batch % 8 == 0)) {
+        // bf16 C [batch][M][N] for the epilogue's bulk stores: 64-column x 32-row boxes, clipped at the edges
+        const uint64_t d[3] = {static_cast<uint64_t>(a->n), static_cast<uint64_t>(a->m), static_cast<uint64_t>(a->batch)};
+        const uint64_t st[2] = {static_cast<uint64_t>(a->stride_c) * 2,
+                                static_cast<uint64_t>(a->batch > 1 ? a->stride_c_batch : a->stride_c * a->m) * 2};
+        const uint32_t bx[3] = {64, 32, 1};
+        if ((rc = make_tmap(&p.tmap_c, a->ptr_c, 3, d, st, bx, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16))) return rc;
+        p.c_tma = 1;
+    }
     p.c = a->ptr_c;
     p.sfa = static_cast<const float*>(a->ptr_sfa);
     p.sfb = static_cast<const float*>(a->ptr_sfb);

@@ -32,11 +32,16 @@ struct PairCfg {
     // barriers, 1 KB of alignment slack
     static constexpr int PER_STAGE = STAGE_BYTES + ((MODE == MODE_BLOCK) ? 1024 : 0);
     static constexpr int OUT_STAGE_BYTES = 8 * kOutStageBytesPerWarp;   // epilogue store staging, one buffer per warp
-    static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES) / PER_STAGE;
+    // block-scale: the whole finished bf16 tile of this CTA (128 x BN) is parked in shared memory and leaves
+    // through TMA bulk stores, so that the epilogue warps never wait for the memory system
+    static constexpr int NCH_ = BN / 2;
+    static constexpr bool TILE_TMA = (MODE == MODE_BLOCK) && (NCH_ % 64 == 0);
+    static constexpr int TILE_STAGE_BYTES = TILE_TMA ? 128 * BN * 2 : 0;
+    static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES - TILE_STAGE_BYTES) / PER_STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SFA_RING = 2 * STAGES;                     // block-scale: slots of 128 fp32 A scales
     static constexpr int SFA_RING_BYTES = (MODE == MODE_BLOCK) ? SFA_RING * 512 : 0;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + OUT_STAGE_BYTES + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + OUT_STAGE_BYTES + TILE_STAGE_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
     static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
@@ -298,6 +303,11 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             ((p.c_batch * esz) % 16 == 0);
         const uint32_t leader_acce0 = mapa_shared(bar_acce0, 0);
         uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 + Cfg::SFA_RING_BYTES + ew * kOutStageBytesPerWarp;
+        // this warp's part of the tile staging area: NCH/64 boxes of 32 rows x 128 bytes (1024-byte aligned)
+        const uint32_t tile_stage = smem_base + STAGES * Cfg::STAGE_BYTES + 1024 + Cfg::SFA_RING_BYTES +
+                                    Cfg::OUT_STAGE_BYTES + ew * (32 * NCH * 2);
+        uint8_t* tile_stage_gen = smem_gen + (tile_stage - smem_base);
+        bool stores_pending = false;
         float tscale = 1.0f;
         if constexpr (MODE == MODE_ACC) {
             if (p.scale_a) tscale *= __ldg(p.scale_a);
@@ -401,7 +411,37 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     B200_TRACE_EPI(2);
                 }
-                if (ok) {
+                if (ok && Cfg::TILE_TMA && p.c_tma) {
+                    // bf16 tile -> shared memory in the 128-byte-swizzled layout of the TMA box (16-byte piece c of
+                    // row r sits at piece c ^ (r & 7): conflict-free for the row-per-lane register layout), then
+                    // one bulk store per 64-column box.  The stores run behind the next tile's work.
+                    if (stores_pending) {
+                        if (lane == 0) bulk_wait_read_all();      // the previous tile's stores have read the buffer
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int q = 0; q < NCH / 8; ++q) {                  // 8 columns = 16 bytes per piece
+                        float o[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) unpack_f32x2(acc[q * 4 + j], o[2 * j], o[2 * j + 1]);
+                        uint4 w;
+                        w.x = pack_bf16x2(o[0], o[1]);
+                        w.y = pack_bf16x2(o[2], o[3]);
+                        w.z = pack_bf16x2(o[4], o[5]);
+                        w.w = pack_bf16x2(o[6], o[7]);
+                        const int box = q >> 3, piece = q & 7;
+                        *reinterpret_cast<uint4*>(tile_stage_gen + box * 4096 + lane * 128 + ((piece ^ (lane & 7)) << 4)) = w;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int box = 0; box < NCH / 64; ++box)
+                            tma_store_3d(&p.tmap_c, tile_stage + box * 4096, col_base + box * 64, row0, b);
+                        bulk_commit_group();
+                    }
+                    stores_pending = true;
+                } else if (ok) {
                     // 64-byte row segments: 32 columns of bf16 or 16 columns of fp32 per pass
                     if (p.out_dtype == OUT_BF16) {
 #pragma unroll
@@ -467,6 +507,8 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
     }
 
     // ---------------------------------- teardown ----------------------------------
+    // (a CTA must not exit while its bulk stores still read its shared memory)
+    if (warp >= 4 && lane == 0) bulk_wait_all();
     tc_fence_before();
     __syncthreads();
     // neither CTA may leave while its partner can still read its shared memory or signal its barriers

@@ -30,6 +30,7 @@ struct GemmParams {
     CUtensorMap tmap_sfa;        // pair kernels.  MX: scale atoms as u8 [atoms*2][256], box 256 x 2.
                                  //   block-scale: fp32 SFA [batch][K/128][M], box 128 x 1 (when sfa_tma != 0)
     CUtensorMap tmap_sfb;        // pair kernels, MX: box 256 x 2*atoms
+    CUtensorMap tmap_c;          // pair kernels, block-scale, bf16 out: C [batch][M][N], box 64 x 32, 128-byte swizzle
     void* c;
     const float* sfa;            // block: fp32 [K/128][M];   MX: E8M0 atoms (uint8, see sf_relayout)
     const float* sfb;            // block: fp32 [N/128][K/128]; MX: E8M0 atoms
@@ -41,6 +42,7 @@ struct GemmParams {
     int tiles_m, tiles_n, tiles_total, kblocks;
     int out_dtype;
     int sfa_tma;                 // block-scale pair kernels: A scales are staged through shared memory by TMA
+    int c_tma;                   // block-scale pair kernels: finished tiles leave through TMA bulk stores
     int* status;
 };
 

@@ -65,11 +65,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // a cluster-scope release here was measured at ~1200 clocks because it waits for every outstanding load of
 // the thread; the hand-offs it is used for are ordered by tcgen05.fence, not by generic-proxy memory.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-#ifdef B200_RELAXED_ARRIVE
-    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-#else
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-#endif
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -195,6 +191,17 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// TMA store shared -> global (bulk async group): out-of-range rows/columns of the box are clipped
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until the bulk stores issued by this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// wait until they are complete (written)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // linear bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile(
