@@ -110,6 +110,8 @@ def cpu_reference_arm(args, workload, rank, world):
     all host cores.  Each step is a bounded row slab of the workload."""
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle import oracle as O
 
     m, n, k = WORKLOADS[workload]
@@ -182,6 +184,7 @@ def main():
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -204,6 +207,10 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # leave 16 SMs to the NCCL kernel of the activation broadcast and keep NCCL within them (config 2 has
+        # 448 pair tiles: 66 resident pairs need the same 7 rounds as 74, so the GEMM loses nothing)
+        os.environ.setdefault("NCCL_MAX_NCHANNELS", "16")
+        os.environ.setdefault("B200GEMM_MAX_SMS", str(torch.cuda.get_device_properties(dev).multi_processor_count - 16))
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
 
@@ -220,41 +227,74 @@ def main():
     qa0, sfa0 = api.quantize_1x128(xa)
     del xa
     sets = []
+    act_bufs = []
     for i in range(nsets):
         # distinct buffers with the same statistics: row-rotated copies of the quantised operands
         sh = (i * 128) % m
-        qa = torch.roll(qa0, sh, 0).contiguous()
-        sfa = torch.roll(sfa0, sh, 1).contiguous()
+        # A and SFA live back to back in one buffer (one broadcast moves both)
+        act = torch.empty(m * k + 4 * kg * m, dtype=torch.uint8, device=dev)
+        qa = act[:m * k].view(m, k)
+        sfa = act[m * k:].view(torch.float32).view(kg, m)
+        qa.copy_(torch.roll(qa0, sh, 0))
+        sfa.copy_(torch.roll(sfa0, sh, 1))
+        act_bufs.append(act)
         shb = (i * 128) % n
         qb = torch.roll(qb0, shb, 0).contiguous()
         sfb = torch.roll(sfb0, shb // 128, 0).contiguous()
         sets.append((qa, sfa, qb, sfb, torch.empty(m, n, dtype=torch.bfloat16, device=dev)))
     torch.cuda.synchronize()
 
-    def step(i):
+    # N-sharded mode: rank 0 owns the activation; A and SFA of a set share one buffer so that one broadcast moves
+    # both.  The broadcast of step i+1 runs on a side stream while the GEMM of step i computes (the GEMM grid
+    # leaves a few SMs to NCCL, see B200GEMM_MAX_SMS); the GEMM of a step waits for its own broadcast.
+    comm = torch.cuda.Stream() if world > 1 else None
+    pending = {}
+    gemm_done = {}
+
+    def post_broadcast(i):
+        qa, sfa, qb, sfb, out = sets[i % nsets]
+        prev = gemm_done.get(i - nsets)
+        with torch.cuda.stream(comm):
+            if prev is not None:
+                comm.wait_event(prev)              # the GEMM that last read this set's activation has finished
+            pending[i] = dist.broadcast(act_bufs[i % nsets], src=0, async_op=True)
+
+    def step(i, last):
         qa, sfa, qb, sfb, out = sets[i % nsets]
         if world > 1:
-            # activation exchange of the sharded path: rank 0 owns A, every rank needs it
-            dist.broadcast(qa, src=0)
-            dist.broadcast(sfa, src=0)
+            if i not in pending:
+                post_broadcast(i)
+            pending.pop(i).wait()                  # the current stream waits for this step's activation
+            if not last:
+                post_broadcast(i + 1)
         api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out=out, tile=args.tile)
+        if world > 1:
+            ev = torch.cuda.Event()
+            ev.record()
+            gemm_done[i] = ev
+            gemm_done.pop(i - 2 * nsets, None)
 
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    step_no = [0]
 
+    def run(count):
+        for j in range(count):
+            step(step_no[0], last=(j == count - 1))
+            step_no[0] += 1
+
+    run(args.warmup)
+    torch.cuda.synchronize()
+    # start the clock sampler BEFORE the barrier: every rank must enter the timed region together
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
     launches0 = api.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        step(i)
+    run(args.steps)
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -328,6 +368,38 @@ def main():
                "h2d_bytes_per_step": int(ha.nbytes + hb.nbytes + hsfa.nbytes + hsfb.nbytes), "d2h_bytes_per_step": int(hcn.nbytes),
                "ms_per_step": ems / esteps, "api": "b200_gemm_a8w8_host (pinned host operands in, bf16 result out)"}
 
+    # ---- skinny-M decode on pre-shuffled weights (config 4), reported as HBM GB/s beside the headline ----
+    decode = None
+    if world == 1 and not args.no_decode:
+        dn, dk = 18432, 7168
+        peaks_hbm = measured_peaks()["hbm_gbs"]
+        wsrc = torch.from_numpy(api.fill_uniform((dn, dk), SEED, 11, -1.0, 1.0)).to(dev)
+        wq, wsf = api.quantize_128x128(wsrc)
+        del wsrc
+        flat = api.shuffle_b(wq, "nk")
+        # four weight images (528 MB) are rotated so that no launch finds its weights in L2
+        flats = [flat] + [torch.roll(flat, 4096 * (j + 1)).contiguous() for j in range(3)]
+        decode = []
+        for dm in (1, 16, 64):
+            xq, xsf = api.quantize_1x128(torch.from_numpy(api.fill_uniform((dm, dk), SEED, 12, -1.0, 1.0)).to(dev))
+            dout = torch.empty(dm, dn, dtype=torch.bfloat16, device=dev)
+            for j in range(8):
+                api.gemm_a8w8_blockscale(xq, flats[j % 4], xsf, wsf, out=dout, b_flat_n=dn)
+            torch.cuda.synchronize()
+            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 200
+            d0.record()
+            for j in range(reps):
+                api.gemm_a8w8_blockscale(xq, flats[j % 4], xsf, wsf, out=dout, b_flat_n=dn)
+            d1.record()
+            torch.cuda.synchronize()
+            us = d0.elapsed_time(d1) / reps * 1e3
+            nbytes = dn * dk + dm * dk + 4 * (dn // 128) * (dk // 128) + 4 * dm * (dk // 128) + 2 * dm * dn
+            gbs = nbytes / us / 1e3
+            decode.append({"m": dm, "n": dn, "k": dk, "us": us, "gbs": gbs, "bytes": nbytes,
+                           "frac_of_measured_hbm": gbs / peaks_hbm, "frac_of_nominal_8000": gbs / 8000.0})
+        del flats, flat, wq
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(args.workload)
@@ -344,6 +416,7 @@ def main():
                        "seed": SEED},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "kernel_ms": kern_ms, "device_status": status,
+            "decode": decode,
         }
         print(json.dumps(line))
     if world > 1:

@@ -9,6 +9,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -68,6 +69,12 @@ int device_state(DeviceState** out) {
         cudaDeviceProp prop;
         CU_TRY(cudaGetDeviceProperties(&prop, dev));
         s.sm_count = prop.multiProcessorCount;
+        // B200GEMM_MAX_SMS caps the SMs the persistent GEMM grids occupy, so that a collective running on another
+        // stream (the activation broadcast of the N-sharded mode) finds free SMs and overlaps with the GEMM
+        if (const char* cap = std::getenv("B200GEMM_MAX_SMS")) {
+            const int v = std::atoi(cap);
+            if (v >= 2 && v < s.sm_count) s.sm_count = v;
+        }
         s.cc_major = prop.major;
         if (prop.major != 10) return B200_ERR_NO_DEVICE;
         void* sym = nullptr;
