@@ -339,11 +339,18 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
         asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 // Pair kernels: arrive on the barrier at offset `bar` in BOTH CTAs of the pair once the MMAs issued so far
-// have completed.  Two plain commits, one per CTA; the partner's barrier is named by its mapa address.
+// have completed.  One commit with a CTA mask (a commit is a completion signal, not a load); every commit is
+// an entry in the tensor queue, and the issuing thread stalls while that queue is full.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+#ifdef B200_PLAIN_PAIR_COMMIT
     const uint32_t b0 = mapa_shared(bar, 0), b1 = mapa_shared(bar, 1);
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b0) : "memory");
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b1) : "memory");
+#else
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+#endif
 }
 __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
     uint32_t v;
