@@ -479,26 +479,52 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
                 constexpr int CW = (NCH % 32 == 0) ? 32 : 16;      // columns per TMEM load
                 constexpr int NC = NCH / CW;
-                float v[2][CW];
-                tmem_ld<CW>(taddr, v[0]);
+                if constexpr (ACC_STAGES == 1) {
+                    // A single accumulator buffer (MX, 256 columns + scale columns fill TMEM): pull this thread's
+                    // whole row slice into registers at once and give the buffer back before converting and
+                    // storing, so the next tile's MMAs run under the stores.
+                    float v[NCH];
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
+                    for (int c = 0; c < NC; ++c) tmem_ld<CW>(taddr + c * CW, &v[c * CW]);
                     tmem_ld_wait();
-                    if (c + 1 < NC) tmem_ld<CW>(taddr + (c + 1) * CW, v[(c + 1) & 1]);
-                    if (c + 1 == NC) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
-                    }
-                    if (MODE == MODE_ACC) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
 #pragma unroll
-                        for (int j = 0; j < CW; ++j) v[c & 1][j] *= tscale;
+                    for (int c = 0; c < NC; ++c) {
+                        if (MODE == MODE_ACC) {
+#pragma unroll
+                            for (int j = 0; j < CW; ++j) v[c * CW + j] *= tscale;
+                        }
+                        if (p.out_dtype == OUT_BF16 || CW == 16) {
+                            store_chunk_coalesced<CW>(p, cbatch, out_stage, row0, col_base + c * CW, &v[c * CW], lane, vec_ok);
+                        } else {
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW, &v[c * CW], lane, vec_ok);
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW + 16, &v[c * CW + 16], lane, vec_ok);
+                        }
                     }
-                    if (p.out_dtype == OUT_BF16 || CW == 16) {
-                        store_chunk_coalesced<CW>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
-                    } else {
-                        store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
-                        store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW + 16, v[c & 1] + 16, lane, vec_ok);
+                } else {
+                    float v[2][CW];
+                    tmem_ld<CW>(taddr, v[0]);
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        tmem_ld_wait();
+                        if (c + 1 < NC) tmem_ld<CW>(taddr + (c + 1) * CW, v[(c + 1) & 1]);
+                        if (c + 1 == NC) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                        }
+                        if (MODE == MODE_ACC) {
+#pragma unroll
+                            for (int j = 0; j < CW; ++j) v[c & 1][j] *= tscale;
+                        }
+                        if (p.out_dtype == OUT_BF16 || CW == 16) {
+                            store_chunk_coalesced<CW>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
+                        } else {
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW, v[c & 1], lane, vec_ok);
+                            store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_base + c * CW + 16, v[c & 1] + 16, lane, vec_ok);
+                        }
                     }
                 }
                 ++phase;
