@@ -95,8 +95,46 @@ int device_state(DeviceState** out) {
 }
 
 // u8 tensor map of rank `rank`; dims/strides innermost first, strides[i] = byte stride of dim i+1
+// Encoding a tensor map costs a driver call; serving loops present the same few buffers over and over, so
+// the most recent encodings are kept (keyed by every encode parameter; a map holds no device-specific state
+// beyond the address it was encoded for).
+struct TmapKey {
+    const void* base;
+    uint64_t dims[5], strides[4];
+    uint32_t box[5];
+    int rank, swz, dtype;
+};
+struct TmapEntry {
+    TmapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int kTmapCache = 64;
+TmapEntry g_tmaps[kTmapCache];
+int g_tmap_next = 0;
+std::mutex g_tmap_mu;
+
 int make_tmap(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
               const uint32_t* box, CUtensorMapSwizzle swz, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8) {
+    TmapKey key;
+    std::memset(&key, 0, sizeof(key));
+    key.base = base;
+    key.rank = rank;
+    key.swz = static_cast<int>(swz);
+    key.dtype = static_cast<int>(dtype);
+    for (int i = 0; i < rank; ++i) {
+        key.dims[i] = dims[i];
+        key.box[i] = box[i];
+    }
+    for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+    {
+        std::lock_guard<std::mutex> lk(g_tmap_mu);
+        for (int i = 0; i < kTmapCache; ++i)
+            if (g_tmaps[i].used && std::memcmp(&g_tmaps[i].key, &key, sizeof(key)) == 0) {
+                *tm = g_tmaps[i].map;
+                return B200_OK;
+            }
+    }
     cuuint64_t gd[5], gs[4];
     cuuint32_t bx[5], es[5];
     for (int i = 0; i < rank; ++i) {
@@ -111,6 +149,14 @@ int make_tmap(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
     if (r != CUDA_SUCCESS) {
         g_last_cuda = 100000 + static_cast<int>(r);
         return B200_ERR_CUDA;
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_tmap_mu);
+        TmapEntry& e = g_tmaps[g_tmap_next];
+        g_tmap_next = (g_tmap_next + 1) % kTmapCache;
+        e.key = key;
+        e.map = *tm;
+        e.used = true;
     }
     return B200_OK;
 }
@@ -246,9 +292,26 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
     return B200_OK;
 }
 
+// (one call per kernel and device: the attribute sticks, and a launch should cost no more host time than it
+// has to.  Keyed by the function address -- every instantiation has the same pointer TYPE.)
+struct SmemAttrDone {
+    const void* fn;
+    int dev;
+};
+SmemAttrDone g_smem_done[256];
+int g_smem_done_count = 0;
+std::mutex g_smem_mu;
+
 template <class Kernel>
 int set_smem(Kernel kernel, int bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B200_ERR_NO_DEVICE;
+    const void* fn = reinterpret_cast<const void*>(kernel);
+    std::lock_guard<std::mutex> lk(g_smem_mu);
+    for (int i = 0; i < g_smem_done_count; ++i)
+        if (g_smem_done[i].fn == fn && g_smem_done[i].dev == dev) return B200_OK;
     CU_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (g_smem_done_count < 256) g_smem_done[g_smem_done_count++] = SmemAttrDone{fn, dev};
     return B200_OK;
 }
 
