@@ -333,8 +333,21 @@ int launch_decode(const DecodeParams& p, int grid, cudaStream_t st) {
     auto kernel = decode_a8w8_sm100_kernel<Cfg>;
     int rc = set_smem(kernel, Cfg::SMEM_BYTES);
     if (rc) return rc;
-    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
-    CU_TRY(cudaGetLastError());
+    // programmatic serialization: a following decode launch may begin (and request its first weight tiles)
+    // while this one drains; the kernel waits for its predecessor before it touches tokens, scales or C
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    std::memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CU_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
     g_launches.fetch_add(1);
     return B200_OK;
 }

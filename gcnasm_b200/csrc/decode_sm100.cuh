@@ -92,6 +92,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
     const int kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
     const int nkb = kb1 - kb0;
 
+    // Consecutive decode GEMMs of a serving step are launched with programmatic serialization: this kernel may
+    // start while its predecessor is still draining.  The weights do not depend on the predecessor, so the first
+    // ring of weight tiles is requested right away; everything that reads the predecessor's output (tokens,
+    // token scales) or writes C comes after pdl_wait().
+    pdl_launch_dependents();
+    const int first = nkb < STAGES ? nkb : STAGES;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full0 + s * 8, 1);
@@ -104,24 +110,34 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
+        for (int i = 0; i < first; ++i) {
+            const uint32_t sw = smem_base + i * Cfg::STAGE_BYTES;
+            const uint32_t full = bar_full0 + i * 8;
+            mbar_arrive_expect_tx(full, Cfg::W_BYTES + Cfg::X_BYTES);
+            if constexpr (Cfg::BLAYOUT == BL_NK)
+                tma_load_3d(sw, &p.tmap_w, full, (kb0 + i) * BK, ni * BNW, b);
+            else
+                tma_load_4d(sw, &p.tmap_w, full, 0, ni * (BNW / 16), (kb0 + i) * (BK / 16), b);
+        }
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
         tmem_relinquish<1>();
     }
-    if (warp == 0 && lane == 0) {
-        prefetch_tmap(&p.tmap_w);
-        prefetch_tmap(&p.tmap_x);
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < first; ++i)
+            tma_load_3d(smem_base + i * Cfg::STAGE_BYTES + Cfg::W_BYTES, &p.tmap_x, bar_full0 + i * 8, (kb0 + i) * BK, 0, b);
+    }
 
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------ TMA producer ------------------------------
-            for (int i = 0; i < nkb; ++i) {
+            for (int i = first; i < nkb; ++i) {
                 const int kb = kb0 + i;
                 const uint32_t s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;

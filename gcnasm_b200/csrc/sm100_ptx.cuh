@@ -210,6 +210,13 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         : "memory");
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------------
+// launch_dependents: the next kernel in the stream (if it was launched with programmatic serialization) may
+// start being scheduled.  wait: block until the previous kernel has completed and its writes are visible;
+// returns at once when there is no such dependency.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- cluster helpers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
