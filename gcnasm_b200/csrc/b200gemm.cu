@@ -375,9 +375,9 @@ int max_pairs(Kernel kernel, int threads, int smem, int sm_count) {
     return n < sm_count / 2 ? n : sm_count / 2;
 }
 
-template <int BN, int MODE, int BL>
+template <int BN, int MODE, int BL, int EW = 8>
 int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
-    using Cfg = PairCfg<BN, MODE, BL>;
+    using Cfg = PairCfg<BN, MODE, BL, EW>;
     auto kernel = gemm_a8w8_pair_sm100_kernel<Cfg>;
     int rc = set_smem(kernel, Cfg::SMEM_BYTES);
     if (rc) return rc;
@@ -600,16 +600,6 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         const uint32_t box_a[2] = {256, 2}, box_b[2] = {256, static_cast<uint32_t>(2 * ((BN + 127) / 128))};
         if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 2, da, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
         if ((rc = make_tmap(&p.tmap_sfb, a->ptr_sfb, 2, db, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-    }
-    if (pair && a->scale_mode == B200_SCALE_BLOCK && aligned16(a->ptr_sfa) && a->stride_sfa % 4 == 0 &&
-        (a->batch == 1 || a->stride_sfa_batch % 4 == 0)) {
-        // fp32 SFA [batch][K/128][M] for the producer's per-group 128-row slices
-        const uint64_t d[3] = {static_cast<uint64_t>(a->m), static_cast<uint64_t>(a->k / 128), static_cast<uint64_t>(a->batch)};
-        const uint64_t st[2] = {static_cast<uint64_t>(a->stride_sfa) * 4,
-                                static_cast<uint64_t>(a->batch > 1 ? a->stride_sfa_batch : a->stride_sfa * (a->k / 128)) * 4};
-        const uint32_t bx[3] = {128, 1, 1};
-        if ((rc = make_tmap(&p.tmap_sfa, a->ptr_sfa, 3, d, st, bx, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32))) return rc;
-        p.sfa_tma = 1;
     }
     if (pair && a->scale_mode == B200_SCALE_BLOCK && a->out_dtype == B200_OUT_BF16 && aligned16(a->ptr_c) &&
         a->stride_c % 8 == 0 && (a->batch == 1 || a->stride_c_batch % 8 == 0)) {

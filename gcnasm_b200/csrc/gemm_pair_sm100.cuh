@@ -18,9 +18,13 @@
 
 namespace b200 {
 
-template <int BN_, int MODE_, int BLAYOUT_>
+// EW_ = epilogue warps per CTA: 8 (two per scheduler, 32 rows x BN/2 columns each) is what the launcher
+// instantiates.  16 (four per scheduler, 32 rows x BN/4 columns, 16-column TMEM loads, 112 registers) computes the
+// same results but measured 1475 against 2010 TFLOP/s on 8192^3 block-scale, so it is not built.
+template <int BN_, int MODE_, int BLAYOUT_, int EW_ = 8>
 struct PairCfg {
     static constexpr int BM = 128, BN = BN_, BK = 128, MODE = MODE_, BLAYOUT = BLAYOUT_;
+    static constexpr int EPI_WARPS = EW_, NSPLIT = EW_ / 4;         // column parts per row quadrant
     static constexpr int BH = BN / 2;                               // B rows loaded by each CTA
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BH * BK;
@@ -28,27 +32,34 @@ struct PairCfg {
     static constexpr int SFA_BYTES = (MODE == MODE_MX) ? 512 : 0;
     static constexpr int SFB_BYTES = (MODE == MODE_MX) ? SFB_ATOMS * 512 : 0;
     static constexpr int STAGE_BYTES = ((A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024) * 1024;
-    // 227 KB per CTA: ring stages (+ two 512-byte A-scale slots per stage in block-scale mode), 1 KB of
-    // barriers, 1 KB of alignment slack
-    static constexpr int PER_STAGE = STAGE_BYTES + ((MODE == MODE_BLOCK) ? 1024 : 0);
-    static constexpr int OUT_STAGE_BYTES = 8 * kOutStageBytesPerWarp;   // epilogue store staging, one buffer per warp
+    // 227 KB per CTA: ring stages, 1 KB of barriers, 1 KB of alignment slack, store staging
     // block-scale: the whole finished bf16 tile of this CTA (128 x BN) is parked in shared memory and leaves
     // through TMA bulk stores, so that the epilogue warps never wait for the memory system
-    static constexpr int NCH_ = BN / 2;
+    static constexpr int NCH_ = BN / NSPLIT;
     static constexpr bool TILE_TMA = (MODE == MODE_BLOCK) && (NCH_ % 64 == 0);
     static constexpr int TILE_STAGE_BYTES = TILE_TMA ? 128 * BN * 2 : 0;
-    static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES - TILE_STAGE_BYTES) / PER_STAGE;
+    // per-warp staging of the plain-store epilogue; with a tile staging area it lives inside that area (a launch
+    // uses one of the two store paths)
+    static constexpr int OUT_STAGE_BYTES = TILE_TMA ? 0 : EW_ * kOutStageBytesPerWarp;
+    static_assert(!TILE_TMA || 32 * NCH_ * 2 >= kOutStageBytesPerWarp, "per-warp tile area holds the plain-store staging");
+    static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES - TILE_STAGE_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SFA_RING = 2 * STAGES;                     // block-scale: slots of 128 fp32 A scales
-    static constexpr int SFA_RING_BYTES = (MODE == MODE_BLOCK) ? SFA_RING * 512 : 0;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SFA_RING_BYTES + OUT_STAGE_BYTES + TILE_STAGE_BYTES + 1024;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + OUT_STAGE_BYTES + TILE_STAGE_BYTES + 1024;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int SF_COLS = (MODE == MODE_MX) ? 4 + 4 * SFB_ATOMS : 0;
     static constexpr int ACC_STAGES = (2 * BN + SF_COLS <= 512) ? 2 : 1;
     static constexpr int ACC_COLS = ACC_STAGES * BN;
     static constexpr int TMEM_COLS = (ACC_COLS + SF_COLS) <= 128 ? 128 : (ACC_COLS + SF_COLS) <= 256 ? 256 : 512;
-    static constexpr int NCH = BN / 2;                              // columns owned by one epilogue thread
-    static constexpr int THREADS = 384;
+    static constexpr int NCH = BN / NSPLIT;                         // columns owned by one epilogue thread
+    static constexpr int THREADS = 128 + 32 * EW_;
+    // setmaxnreg only redistributes the registers the CTA got at launch (THREADS x the per-thread count the
+    // launch bound allows, a multiple of 8); an increase beyond that pool blocks forever
+    static constexpr int ROLE_REGS = (EW_ == 8) ? 40 : 32, EPI_REGS = (EW_ == 8) ? 232 : 112;
+    static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;
+    static_assert(128 * ROLE_REGS + 32 * EW_ * EPI_REGS <= THREADS * LAUNCH_REGS, "setmaxnreg pool");
+    static constexpr int LW = (EW_ == 8) ? 32 : 16;                 // columns per TMEM load in block-scale mode
+    static_assert(EW_ == 8 || EW_ == 16, "8 or 16 epilogue warps");
+    static_assert(EW_ == 8 || (MODE == MODE_BLOCK && BN % 64 == 0), "16 epilogue warps: block-scale tiles only");
     static_assert(BN % 32 == 0 && BN <= 256 && BN >= 64, "pair tile N: multiple of 32 in [64, 256]");
     static_assert(MODE != MODE_BLOCK || ACC_STAGES == 2, "block-scale needs two partial buffers");
     static_assert(MODE != MODE_MX || BN % 128 == 0, "MX scale atoms cover 128 columns");
@@ -87,16 +98,22 @@ static constexpr int kBlockIssuers = 2;
 __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
 #define B200_TRACE_EPI(slot)                                                                     \
     do {                                                                                         \
-        if (pair_id == 0 && lane == 0 && phase < 128)                                            \
+        if (pair_id == 0 && lane == 0 && phase < 128 && ew < 8)                                  \
             g_trace[((static_cast<int>(cta) * 8 + ew) * 128 + phase) * 8 + (slot)] = clock64();   \
     } while (0)
 #define B200_TRACE_MMA(slot)                                                                     \
     do {                                                                                         \
         if (pair_id == 0 && phase < 128) g_trace[2 * 8 * 128 * 8 + phase * 8 + (slot)] = clock64(); \
     } while (0)
+// the producers' stamps share the issuer rows: slots 6 and 7 of row it (leader CTA only)
+#define B200_TRACE_PROD(slot)                                                                    \
+    do {                                                                                         \
+        if (pair_id == 0 && cta == 0 && warp == 0 && it < 128) g_trace[2 * 8 * 128 * 8 + it * 8 + 6 + (slot)] = clock64(); \
+    } while (0)
 #else
 #define B200_TRACE_EPI(slot)
 #define B200_TRACE_MMA(slot)
+#define B200_TRACE_PROD(slot)
 #endif
 
 template <class Cfg>
@@ -115,10 +132,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t bar_acce0 = bar_accf0 + 2 * 8;                       // used in the leader only
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // block-scale: ring of A-scale slots (128 fp32 each) filled by the producer, one barrier per slot
-    const uint32_t bar_sf0 = bar_acce0 + 2 * 8 + 8;
-    const uint32_t sfa_ring0 = bar_full0 + 1024;
-    const float* sfa_ring = reinterpret_cast<const float*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 1024);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -134,10 +147,8 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar_accf0 + s * 8, 1);          // one tcgen05.commit per use
-            mbar_init(bar_acce0 + s * 8, 16);         // 8 epilogue warps in each of the two CTAs
+            mbar_init(bar_acce0 + s * 8, 2 * Cfg::EPI_WARPS);   // every epilogue warp of the two CTAs
         }
-        if constexpr (MODE == MODE_BLOCK)
-            for (int s = 0; s < Cfg::SFA_RING; ++s) mbar_init(bar_sf0 + s * 8, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -167,7 +178,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
     if (!tmem_ok) {
         // fall through to the teardown
     } else if (warp < 4) {
-        setmaxnreg_dec<40>();
+        setmaxnreg_dec<Cfg::ROLE_REGS>();
         if (warp == 0 && lane == 0) {
             // ------------------------------ TMA producer (both CTAs) ------------------------------
             uint32_t it = 0;
@@ -187,6 +198,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
+                    B200_TRACE_PROD(0);
                     if (cta == 0)
                         mbar_arrive_expect_tx(bar_full0 + s * 8,
                                               2 * (Cfg::A_BYTES + Cfg::B_BYTES + Cfg::SFA_BYTES + Cfg::SFB_BYTES));
@@ -196,16 +208,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, b);
                     else
                         tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), b);
-                    if constexpr (MODE == MODE_BLOCK) {
-                        if (p.sfa_tma) {
-                            // this CTA's 128 A scales of K group kb -> slot it % (2*STAGES).  Twice as many slots
-                            // as stages: a slot is rewritten only after the MMAs of STAGES groups later have
-                            // started, long after the epilogue read it.
-                            const uint32_t slot = it % Cfg::SFA_RING;
-                            mbar_arrive_expect_tx(bar_sf0 + slot * 8, 512);
-                            tma_load_3d(sfa_ring0 + slot * 512, &p.tmap_sfa, bar_sf0 + slot * 8, row_a, kb, b);
-                        }
-                    }
+                    B200_TRACE_PROD(1);
                     if constexpr (MODE == MODE_MX) {
                         // scale atoms [batch][K/128][rows/128][512 B], addressed as rows of 256 bytes
                         const long long atom_a = b * (p.sfa_batch >> 9) + static_cast<long long>(kb) * p.sfa_stride + (mi * 2 + cta);
@@ -283,7 +286,9 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                 umma_f8<2>(tacc, da, db, idesc, accum);
                             }
                         }
+                        B200_TRACE_MMA(4);
                         umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
+                        B200_TRACE_MMA(5);
                     }
                     if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs
                     B200_TRACE_MMA(3);
@@ -292,7 +297,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         }
     } else {
         // ---------------------------------- epilogue (both CTAs) ----------------------------------
-        setmaxnreg_inc<232>();
+        setmaxnreg_inc<Cfg::EPI_REGS>();
         const int ew = warp - 4;
         const int quad = warp & 3;
         const int half = ew >> 2;
@@ -302,9 +307,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && ((p.ldc * esz) % 16 == 0) &&
                             ((p.c_batch * esz) % 16 == 0);
         const uint32_t leader_acce0 = mapa_shared(bar_acce0, 0);
-        uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 + Cfg::SFA_RING_BYTES + ew * kOutStageBytesPerWarp;
+        uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 +
+                             (Cfg::TILE_TMA ? ew * (32 * NCH * 2) : ew * kOutStageBytesPerWarp);
         // this warp's part of the tile staging area: NCH/64 boxes of 32 rows x 128 bytes (1024-byte aligned)
-        const uint32_t tile_stage = smem_base + STAGES * Cfg::STAGE_BYTES + 1024 + Cfg::SFA_RING_BYTES +
+        const uint32_t tile_stage = smem_base + STAGES * Cfg::STAGE_BYTES + 1024 +
                                     Cfg::OUT_STAGE_BYTES + ew * (32 * NCH * 2);
         uint8_t* tile_stage_gen = smem_gen + (tile_stage - smem_base);
         bool stores_pending = false;
@@ -336,21 +342,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 const bool col_ok = col_base < p.n;
                 const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
                 const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(blk0) * p.sfb_stride;
-                const bool sfa_tma = p.sfa_tma != 0;
-                float sa_cur = sfa_tma ? 0.0f : __ldg(sfa_p);
+                float sa_cur = __ldg(sfa_p);
                 float sb0_cur = col_ok ? __ldg(sfb_p) : 0.0f;
                 float sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
                 for (int g = 0; g < groups; ++g, ++phase) {
-                    if (sfa_tma) {
-                        // staged by the producer; its barrier completed long before the MMAs of this group ran
-                        const uint32_t slot = phase % Cfg::SFA_RING;
-                        if (!mbar_wait<false, 0>(bar_sf0 + slot * 8, (phase / Cfg::SFA_RING) & 1, abort_flag, p.status,
-                                                 KSTAT_TIMEOUT_FULL)) {
-                            ok = false;
-                            break;
-                        }
-                        sa_cur = sfa_ring[slot * 128 + quad * 32 + lane];
-                    }
                     const float s0 = sa_cur * sb0_cur, s1 = kStraddle ? sa_cur * sb1_cur : s0;
                     const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
                     const uint32_t as = phase & 1;
@@ -367,20 +362,46 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     // when NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load
                     // has landed, before the last FMAs; the next group's scales are fetched after that arrive
                     // (an arrive waits for the thread's outstanding loads).
-                    constexpr int C32 = NCH / 32, TAIL = NCH % 32;
-                    constexpr int NLD = C32 + (TAIL ? 1 : 0);            // loads per group
-                    float v[2][32];
-                    tmem_ld32(taddr, v[0]);
+                    constexpr int LW = Cfg::LW;                          // columns per load: 32, or 16 with 16 warps
+                    constexpr int CFULL = NCH / LW, TAIL = NCH % LW;
+                    constexpr int NLD = CFULL + (TAIL ? 1 : 0);          // loads per group
+                    static_assert(TAIL == 0 || (LW == 32 && TAIL == 16), "tail load is 16 columns");
+                    float v[2][LW];
+                    tmem_ld<LW>(taddr, v[0]);
                     if (NLD > 1) {
-                        if (C32 > 1) tmem_ld32(taddr + 32, v[1]);
-                        else tmem_ld16(taddr + 32, v[1]);
+                        if (CFULL > 1) tmem_ld<LW>(taddr + LW, v[1]);
+                        else tmem_ld16(taddr + LW, v[1]);
                     }
+                    // tcgen05.wait::ld waits for every load in flight, so it is executed only before the even
+                    // chunks: an odd chunk landed with its predecessor, and a wait there would stall on the
+                    // refill load issued a moment earlier
+                    auto fma_chunk = [&](const int c) {
+                        const unsigned long long scA = (!kStraddle || c * LW < split) ? sc0 : sc1;
+                        const unsigned long long scB = (!kStraddle || c * LW + 16 < split) ? sc0 : sc1;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            acc[c * (LW / 2) + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), scA, acc[c * (LW / 2) + j]);
+                        if constexpr (LW == 32) {
+                            if (c < CFULL) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
+                            }
+                        }
+                    };
+                    auto load_chunk = [&](const int c) {
+                        if (c < CFULL) tmem_ld<LW>(taddr + c * LW, v[c & 1]);
+                        else tmem_ld16(taddr + c * LW, v[c & 1]);
+                    };
+                    constexpr int REL = (NLD - 1) & ~1;                  // the wait at this chunk covers the final load
 #pragma unroll
                     for (int c = 0; c < NLD; ++c) {
-                        tmem_ld_wait();                                  // every load issued so far (up to c+1) has landed
-                        if (c == 0) B200_TRACE_EPI(3);
-                        if (c == (NLD >= 2 ? NLD - 2 : 0)) {
-                            // the final load is among them: hand the TMEM buffer back, then fetch the next scales
+                        if ((c & 1) == 0) {
+                            tmem_ld_wait();                              // chunks c and c+1 have landed
+                            if (c == 0) B200_TRACE_EPI(3);
+                        }
+                        if (c == REL) {
+                            // every load has landed: hand the TMEM buffer back, then fetch the next scales
                             B200_TRACE_EPI(4);
                             tc_fence_before();
                             __syncwarp();
@@ -388,26 +409,14 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
                             B200_TRACE_EPI(1);
                             if (g + 1 < groups) {
-                                if (!sfa_tma) sa_cur = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
+                                sa_cur = __ldg(sfa_p + static_cast<long long>(g + 1) * p.sfa_stride);
                                 sb0_cur = col_ok ? __ldg(sfb_p + g + 1) : 0.0f;
                                 if (kStraddle) sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride + g + 1) : 0.0f;
                             }
                         }
-                        const unsigned long long scA = (!kStraddle || c * 32 < split) ? sc0 : sc1;
-                        const unsigned long long scB = (!kStraddle || c * 32 + 16 < split) ? sc0 : sc1;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            acc[c * 16 + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), scA, acc[c * 16 + j]);
-                        if (c < C32) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
-                        }
-                        // refill the buffer just consumed with chunk c+2
-                        if (c + 2 < NLD) {
-                            if (c + 2 < C32) tmem_ld32(taddr + (c + 2) * 32, v[c & 1]);
-                            else tmem_ld16(taddr + (c + 2) * 32, v[c & 1]);
-                        }
+                        fma_chunk(c);
+                        // refill the buffer just drained; the load runs behind the next chunk's FMAs
+                        if (c + 2 < NLD) load_chunk(c + 2);
                     }
                     B200_TRACE_EPI(2);
                 }
@@ -441,6 +450,11 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                         bulk_commit_group();
                     }
                     stores_pending = true;
+#ifdef B200_TRACE
+                    --phase;
+                    B200_TRACE_EPI(7);     // end of the store phase, filed under the tile's last group
+                    ++phase;
+#endif
                 } else if (ok) {
                     // 64-byte row segments: 32 columns of bf16 or 16 columns of fp32 per pass
                     if (p.out_dtype == OUT_BF16) {

@@ -27,8 +27,7 @@ enum : int { OUT_F32 = 0, OUT_BF16 = 1 };
 struct GemmParams {
     CUtensorMap tmap_a;          // u8 [batch][M][K], box 128 x 128, 128-byte swizzle
     CUtensorMap tmap_b;          // u8 [batch][N][K] (same box) or the flat 4-D view
-    CUtensorMap tmap_sfa;        // pair kernels.  MX: scale atoms as u8 [atoms*2][256], box 256 x 2.
-                                 //   block-scale: fp32 SFA [batch][K/128][M], box 128 x 1 (when sfa_tma != 0)
+    CUtensorMap tmap_sfa;        // pair kernels, MX: scale atoms as u8 [atoms*2][256], box 256 x 2
     CUtensorMap tmap_sfb;        // pair kernels, MX: box 256 x 2*atoms
     CUtensorMap tmap_c;          // pair kernels, block-scale, bf16 out: C [batch][M][N], box 64 x 32, 128-byte swizzle
     void* c;
@@ -41,7 +40,6 @@ struct GemmParams {
     int m, n, k, batch;
     int tiles_m, tiles_n, tiles_total, kblocks;
     int out_dtype;
-    int sfa_tma;                 // block-scale pair kernels: A scales are staged through shared memory by TMA
     int c_tma;                   // block-scale pair kernels: finished tiles leave through TMA bulk stores
     int* status;
 };
