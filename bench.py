@@ -413,6 +413,28 @@ def main():
                            "frac_of_measured_hbm": gbs / peaks_hbm, "frac_of_nominal_8000": gbs / 8000.0})
         del flats, flat, wq
 
+    # ---- fused activation quantiser (bf16 -> e4m3 + [K/128][M] scales), config 5's activation matrix ----
+    act_quant = None
+    if world == 1 and not args.no_decode:
+        am, ak = 16384, 8192
+        xb = torch.randn(am, ak, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        aq = torch.empty(am, ak, dtype=torch.uint8, device=dev)
+        asf = torch.empty(ak // 128, am, dtype=torch.float32, device=dev)
+        for _ in range(3):
+            api.quantize_act_bf16_1x128(xb, q=aq, sfa=asf)
+        torch.cuda.synchronize()
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for _ in range(20):
+            api.quantize_act_bf16_1x128(xb, q=aq, sfa=asf)
+        q1.record()
+        torch.cuda.synchronize()
+        qus = q0.elapsed_time(q1) / 20 * 1e3
+        qbytes = am * ak * 3 + 4 * am * (ak // 128)            # bf16 in, e4m3 out, fp32 scales out: 407 MB > L2
+        act_quant = {"m": am, "k": ak, "us": qus, "bytes": qbytes, "gbs": qbytes / qus / 1e3,
+                     "frac_of_measured_hbm": qbytes / qus / 1e3 / measured_peaks()["hbm_gbs"]}
+        del xb, aq, asf
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(args.workload)
@@ -429,7 +451,7 @@ def main():
                        "seed": SEED},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "kernel_ms": kern_ms, "device_status": status,
-            "decode": decode,
+            "decode": decode, "act_quant": act_quant,
         }
         print(json.dumps(line))
     if world > 1:

@@ -229,6 +229,37 @@ def quantize_mx32(x):
     return q, sf, atoms
 
 
+def quantize_act_bf16_1x128(x, q=None, sfa=None):
+    """Fused activation quantiser: bf16 [M,K] (rows may be strided) -> (q [M,K] uint8, sfa [K/128, M] fp32) in one
+    pass.  `q` / `sfa` may be preallocated views (e.g. slices of a broadcast buffer); q rows may be strided."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a 2-D bf16 tensor with unit column stride")
+    m, k = x.shape
+    if q is None:
+        q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    if sfa is None:
+        sfa = torch.empty((k // 128, m), dtype=torch.float32, device=x.device)
+    if q.shape != (m, k) or q.dtype != torch.uint8 or q.stride(1) != 1:
+        raise ValueError("q must be a [M,K] uint8 tensor with unit column stride")
+    if sfa.shape != (k // 128, m) or sfa.dtype != torch.float32 or sfa.stride(1) != 1:
+        raise ValueError("sfa must be a [K/128, M] fp32 tensor with unit column stride")
+    check(lib().b200_quantize_act_bf16_1x128(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), sfa.data_ptr(),
+                                             sfa.stride(0) if k > 128 else m, m, k, _stream()), "b200_quantize_act_bf16_1x128")
+    return q, sfa
+
+
+def quantize_act_bf16_mx32(x):
+    """Fused MX activation quantiser: bf16 [R,K] -> (q [R,K] uint8, scale atoms for the MX GEMM) in one pass."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a 2-D bf16 tensor with unit column stride")
+    r, k = x.shape
+    q = torch.empty((r, k), dtype=torch.uint8, device=x.device)
+    atoms = torch.empty(lib().b200_mx_sf_bytes(r, k), dtype=torch.uint8, device=x.device)
+    check(lib().b200_quantize_act_bf16_mx32(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), atoms.data_ptr(), r, k,
+                                            _stream()), "b200_quantize_act_bf16_mx32")
+    return q, atoms
+
+
 # ---- seeded inputs (host) ---------------------------------------------------------------------------
 def fill_uniform(shape, seed: int, tensor_id: int, lo: float, hi: float) -> np.ndarray:
     out = np.empty(shape, np.float32)

@@ -186,6 +186,137 @@ __global__ void quant_1x128_kernel(const float* __restrict__ x, uint8_t* __restr
     if (lane == 0) sfa[g * M + row] = s;
 }
 
+// x / s, correctly rounded, for many x and one s.  With r = RN(1/s): q0 = RN(x*r), rem = x - q0*s (exact in an
+// FMA), q = RN(q0 + rem*r) is the correctly rounded quotient when nothing overflows or loses bits to underflow
+// (Markstein).  `fast` (uniform per group) says s is a normal number of moderate size; the callers guarantee
+// |x| <= 448*s*(1+2^-23), and a quotient too small to be exact becomes a zero byte either way.  Everything else takes
+// the IEEE division.
+__device__ __forceinline__ float div_by_scale(float x, float s, float r, bool fast) {
+    if (fast) {
+        const float q0 = __fmul_rn(x, r);
+        return __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
+    }
+    return __fdiv_rn(x, s);
+}
+
+// Fused activation quantiser: bf16 [M][K] (row pitch ldx) -> e4m3 [M][K] (row pitch ldq) + fp32 scales in the
+// GEMM's [K/128][M] layout (group pitch stride_sfa), one pass.  A block covers 32 rows x 16 K groups; warp w walks
+// the 32 rows of groups g0+2w and g0+2w+1 (512 contiguous bytes per row: lanes 0-15 the first group, 16-31 the
+// second, 16 bytes = 8 values per lane) and lane r keeps the two scales of row r, so that the scales leave as two
+// 128-byte lines per warp.  Same arithmetic as the fp32 quantiser: scale = amax/448 (1 for an all-zero group),
+// q = e4m3(x / scale), both divisions correctly rounded.
+__global__ void __launch_bounds__(256) act_quant_bf16_1x128_kernel(const uint16_t* __restrict__ x, long long ldx,
+                                                                   uint8_t* __restrict__ q, long long ldq,
+                                                                   float* __restrict__ sfa, long long stride_sfa,
+                                                                   long long M, long long K) {
+    const long long KG = K >> 7;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long gpair = (static_cast<long long>(blockIdx.x) * 8 + warp) * 2;     // first of the warp's two groups
+    const long long row0 = static_cast<long long>(blockIdx.y) * 32;
+    if (gpair >= KG) return;
+    const bool live = gpair + (lane >> 4) < KG;                  // the second group may not exist
+    const int nrows = (M - row0) < 32 ? static_cast<int>(M - row0) : 32;
+    float my_a = 1.0f, my_b = 1.0f;
+#pragma unroll 1
+    for (int r0 = 0; r0 < nrows; r0 += 4) {
+        uint4 raw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            raw[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (live && r0 + i < nrows)
+                raw[i] = __ldg(reinterpret_cast<const uint4*>(x + (row0 + r0 + i) * ldx + gpair * 128) + lane);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (r0 + i >= nrows) break;                                  // uniform across the warp
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+            float v[8];
+            float m = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                m = fmaxf(m, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            const float sc = m > 0.0f ? __fdiv_rn(m, 448.0f) : 1.0f;     // one per half-warp
+            const float rc = __frcp_rn(sc);
+            const bool fast = sc >= 0x1p-100f && sc <= 0x1p100f;
+            auto dv = [&](float val) { return div_by_scale(val, sc, rc, fast); };
+            uint2 out;
+            out.x = f32x4_to_e4m3x4(dv(v[0]), dv(v[1]), dv(v[2]), dv(v[3]));
+            out.y = f32x4_to_e4m3x4(dv(v[4]), dv(v[5]), dv(v[6]), dv(v[7]));
+            if (live) reinterpret_cast<uint2*>(q + (row0 + r0 + i) * ldq + gpair * 128)[lane] = out;
+            const float sa = __shfl_sync(0xFFFFFFFFu, sc, 0), sb = __shfl_sync(0xFFFFFFFFu, sc, 16);
+            if (lane == r0 + i) {
+                my_a = sa;
+                my_b = sb;
+            }
+        }
+    }
+    if (lane < nrows) {
+        sfa[gpair * stride_sfa + row0 + lane] = my_a;
+        if (gpair + 1 < KG) sfa[(gpair + 1) * stride_sfa + row0 + lane] = my_b;
+    }
+}
+
+// Fused MX activation quantiser: bf16 [rows][K] -> e4m3 [rows][K] + E8M0 scales written straight into the
+// tensor-core atom order [K/128][ceil(rows/128)][32][4][4] (what quant_mx32 followed by mx_sf_relayout produce).
+// Same block shape as above: warp w owns K group g0+w of the block's 32 rows; eight lanes share one 32-wide
+// scale block; lane r keeps the four scale bytes of row r as one word.  Rows of the last atom beyond `rows`
+// get 127 (scale 1.0).  grid.y covers ceil(rows/128)*4 row blocks.
+__global__ void __launch_bounds__(256) act_quant_bf16_mx32_kernel(const uint16_t* __restrict__ x, long long ldx,
+                                                                  uint8_t* __restrict__ q, long long ldq,
+                                                                  uint32_t* __restrict__ atoms, long long rows,
+                                                                  long long K) {
+    const long long KG = K >> 7;
+    const long long R128 = (rows + 127) >> 7;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long g = static_cast<long long>(blockIdx.x) * 8 + warp;
+    const long long row0 = static_cast<long long>(blockIdx.y) * 32;
+    if (g >= KG) return;
+    const int nrows = row0 >= rows ? 0 : ((rows - row0) < 32 ? static_cast<int>(rows - row0) : 32);
+    uint32_t my_word = 0x7F7F7F7Fu;
+#pragma unroll 1
+    for (int r0 = 0; r0 < nrows; r0 += 4) {
+        uint2 raw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            raw[i] = make_uint2(0u, 0u);
+            if (r0 + i < nrows) raw[i] = __ldg(reinterpret_cast<const uint2*>(x + (row0 + r0 + i) * ldx + g * 128) + lane);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (r0 + i >= nrows) break;                                  // uniform across the warp
+            const float a = __uint_as_float(raw[i].x << 16), b = __uint_as_float(raw[i].x & 0xFFFF0000u);
+            const float c = __uint_as_float(raw[i].y << 16), d = __uint_as_float(raw[i].y & 0xFFFF0000u);
+            float m = fmaxf(fmaxf(fabsf(a), fabsf(b)), fmaxf(fabsf(c), fabsf(d)));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+            uint32_t packed;
+            int byte = 0;
+            if (!(m > 0.0f)) {
+                packed = ((__float_as_uint(a) >> 24) & 0x80u) | (((__float_as_uint(b) >> 24) & 0x80u) << 8) |
+                         (((__float_as_uint(c) >> 24) & 0x80u) << 16) | (((__float_as_uint(d) >> 24) & 0x80u) << 24);
+            } else {
+                byte = ilogbf(m) - 8 + 127;
+                byte = byte < 0 ? 0 : (byte > 254 ? 254 : byte);
+                const int e = byte - 127;
+                packed = f32x4_to_e4m3x4(scalbnf(a, -e), scalbnf(b, -e), scalbnf(c, -e), scalbnf(d, -e));
+            }
+            reinterpret_cast<uint32_t*>(q + (row0 + r0 + i) * ldq + g * 128)[lane] = packed;
+            const uint32_t word = static_cast<uint32_t>(__shfl_sync(0xFFFFFFFFu, byte, 0)) |
+                                  (static_cast<uint32_t>(__shfl_sync(0xFFFFFFFFu, byte, 8)) << 8) |
+                                  (static_cast<uint32_t>(__shfl_sync(0xFFFFFFFFu, byte, 16)) << 16) |
+                                  (static_cast<uint32_t>(__shfl_sync(0xFFFFFFFFu, byte, 24)) << 24);
+            if (lane == r0 + i) my_word = word;
+        }
+    }
+    const long long row = row0 + lane;                                   // row0 is a multiple of 32
+    atoms[(g * R128 + (row >> 7)) * 128 + lane * 4 + ((row & 127) >> 5)] = my_word;
+}
+
 // one 256-thread block per 128x128 block; the block stays in registers between amax and quantise
 __global__ void quant_128x128_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ sfb,
                                      long long N, long long K) {

@@ -886,6 +886,49 @@ int b200_quantize_1x128(const float* x, void* q, float* sfa, int64_t m, int64_t 
     g_launches.fetch_add(1);
     return B200_OK;
 }
+int b200_quantize_act_bf16_1x128(const void* x_bf16, int64_t ldx, void* q, int64_t ldq, float* sfa, int64_t stride_sfa,
+                                 int64_t m, int64_t k, void* stream) {
+    if (!x_bf16 || !q || !sfa || m <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (ldx < k || ldq < k || stride_sfa < m) return B200_ERR_BAD_ARG;
+    // 16-byte loads of eight bf16 and 8-byte stores of eight e4m3: pitches and bases must keep that alignment
+    if (k % 128 != 0 || ldx % 8 != 0 || ldq % 8 != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 15) ||
+        (reinterpret_cast<uintptr_t>(q) & 7))
+        return B200_ERR_UNSUPPORTED;
+    const int64_t gx = (k / 128 + 15) / 16, gy = (m + 31) / 32;
+    if (gy > 65535) {
+        // rows beyond the grid's y range: run in slabs of 65535 x 32 rows
+        int rc = B200_OK;
+        const int64_t slab = 65535LL * 32;
+        for (int64_t r = 0; r < m && rc == B200_OK; r += slab) {
+            const int64_t mm = (m - r) < slab ? (m - r) : slab;
+            rc = b200_quantize_act_bf16_1x128(static_cast<const uint16_t*>(x_bf16) + r * ldx, ldx, static_cast<uint8_t*>(q) + r * ldq,
+                                              ldq, sfa + r, stride_sfa, mm, k, stream);
+        }
+        return rc;
+    }
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    act_quant_bf16_1x128_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x_bf16), ldx, static_cast<uint8_t*>(q), ldq, sfa, stride_sfa, m, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_quantize_act_bf16_mx32(const void* x_bf16, int64_t ldx, void* q, int64_t ldq, void* sf_atoms, int64_t rows, int64_t k,
+                                void* stream) {
+    if (!x_bf16 || !q || !sf_atoms || rows <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (ldx < k || ldq < k) return B200_ERR_BAD_ARG;
+    if (k % 128 != 0 || ldx % 4 != 0 || ldq % 4 != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 7) ||
+        (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(sf_atoms) & 3))
+        return B200_ERR_UNSUPPORTED;
+    const int64_t gx = (k / 128 + 7) / 8, gy = ((rows + 127) / 128) * 4;
+    if (gy > 65535) return B200_ERR_TOO_LARGE;          // more than 2,097,120 rows
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    act_quant_bf16_mx32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x_bf16), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint32_t*>(sf_atoms), rows, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
 int b200_quantize_128x128(const float* x, void* q, float* sfb, int64_t n, int64_t k, void* stream) {
     if (!x || !q || !sfb || n <= 0 || k <= 0) return B200_ERR_BAD_ARG;
     if (n % 128 != 0 || k % 128 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3)) return B200_ERR_UNSUPPORTED;

@@ -131,6 +131,16 @@ int b200_quantize_1x128(const float* x, void* q, float* sfa, int64_t m, int64_t 
 int b200_quantize_128x128(const float* x, void* q, float* sfb, int64_t n, int64_t k, void* cuda_stream); /* sfb [N/128][K/128] */
 /* MX 1x32: e = floor(log2(amax)) - 8, byte = clamp(e + 127, 0, 254), q = e4m3(x * 2^-e); sf is [rows][K/32] */
 int b200_quantize_mx32(const float* x, void* q, void* sf, int64_t rows, int64_t k, void* cuda_stream);
+/* Fused activation quantisers: bf16 activations -> e4m3 operand + scales in the layout the GEMM reads, one pass
+ * (no fp32 staging copy, no separate re-layout).  The reference names the scale layout
+ * (block_scale_gemm/README.md:21,28: SFA is [K/128][M], M contiguous) but has no quantiser; same rules as above.
+ * ldx/ldq: row pitches in elements (>= k); stride_sfa: pitch between K groups (>= m); k % 128 == 0.
+ * 1x128: ldx, ldq multiples of 8, x 16-byte and q 8-byte aligned.  MX: multiples of 4, x 8-byte, q 4-byte.  */
+int b200_quantize_act_bf16_1x128(const void* x_bf16, int64_t ldx, void* q, int64_t ldq, float* sfa, int64_t stride_sfa,
+                                 int64_t m, int64_t k, void* cuda_stream);
+/* MX 1x32 scales written directly as atoms (b200_mx_sf_bytes(rows, k) bytes), padding rows = 127 */
+int b200_quantize_act_bf16_mx32(const void* x_bf16, int64_t ldx, void* q, int64_t ldq, void* sf_atoms, int64_t rows,
+                                int64_t k, void* cuda_stream);
 /* Re-lays logical E8M0 scales [rows][K/32] into the tensor-core atom order the MX GEMM reads:
  * [K/128][ceil(rows/128)][32][4][4] bytes, padded rows = 127 (scale 1.0).  Size: b200_mx_sf_bytes().     */
 int b200_mx_sf_relayout(const void* sf_logical, void* sf_atoms, int64_t rows, int64_t k, void* cuda_stream);
