@@ -28,7 +28,7 @@ class ColumnShardedGemm:
     """Holds one rank's weight shard; ``__call__`` broadcasts the activation and runs the local GEMM."""
 
     def __init__(self, b_shard: torch.Tensor, sfb_shard: torch.Tensor, n_total: int, group=None,
-                 gemm_fn: Optional[Callable] = None, out_dtype=torch.bfloat16):
+                 gemm_fn: Optional[Callable] = None, out_dtype=torch.bfloat16, quant_fn: Optional[Callable] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -44,6 +44,13 @@ class ColumnShardedGemm:
 
             gemm_fn = lambda a, b, sfa, sfb, out: api.gemm_a8w8_blockscale(a, b, sfa, sfb, out=out, out_dtype=self.out_dtype)
         self.gemm_fn = gemm_fn
+        if quant_fn is None:
+            def quant_fn(x, q, sfa):
+                from . import api
+
+                api.quantize_act_bf16_1x128(x, q=q, sfa=sfa)
+        self.quant_fn = quant_fn
+        self._act_buf = None
 
     def broadcast_activation(self, a: torch.Tensor, sfa: torch.Tensor, root: int = 0):
         """A [M,K] e4m3 bytes and SFA [K/128, M]: valid on ``root``, allocated (same shape) elsewhere."""
@@ -68,3 +75,29 @@ class ColumnShardedGemm:
         else:
             full[0] = out
         return full
+
+    def activation_buffer(self, m: int, k: int, device) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """One flat buffer ``[M*K e4m3 bytes | (K/128)*M fp32 scales]`` and its two views.  Kept between calls."""
+        need = m * k + 4 * (k // 128) * m
+        if self._act_buf is None or self._act_buf.numel() != need or self._act_buf.device != torch.device(device):
+            self._act_buf = torch.empty(need, dtype=torch.uint8, device=device)
+        buf = self._act_buf
+        return buf, buf[:m * k].view(m, k), buf[m * k:].view(torch.float32).view(k // 128, m)
+
+    def forward_bf16(self, x: Optional[torch.Tensor], m: int, k: int, device, root: int = 0,
+                     out: Optional[torch.Tensor] = None, gather: bool = False):
+        """bf16 activations ``x`` [M,K] (needed on ``root`` only) -> this rank's ``C[:, shard]``.
+
+        The root quantises straight into the broadcast buffer (fused quantiser: one read of x, one write of the
+        e4m3 bytes and of the scales in the GEMM's layout), the buffer travels as ONE broadcast, and every rank runs
+        its GEMM on views of it: no fp32 copy of the activations, no separate scale tensor on the wire."""
+        if m * k % 4 != 0:
+            raise ValueError("M*K must be a multiple of 4 (the scales follow the bytes in one buffer)")
+        buf, a, sfa = self.activation_buffer(m, k, device)
+        if self.rank == root:
+            if x is None or tuple(x.shape) != (m, k):
+                raise ValueError("the root needs the [M,K] activations")
+            self.quant_fn(x, a, sfa)
+        if self.world > 1:
+            dist.broadcast(buf, src=root, group=self.group)
+        return self(a, sfa, root=root, out=out, gather=gather, broadcast=False)

@@ -112,3 +112,19 @@ def test_act_quant_feeds_blockscale_gemm(api, O):
     out = api.gemm_a8w8_blockscale(qa, T(qb), sfa, T(sfb), out_dtype=torch.bfloat16)
     ref = O.gemm_ref_blockscale(qa.cpu().numpy(), qb, sfa.cpu().numpy(), sfb)
     assert_close(O, out.float().cpu().numpy(), ref)
+
+
+def test_sharded_forward_bf16_single_gpu(api, O):
+    """The sharded operator's bf16 entry on one GPU (world 1): fused quantise into the broadcast buffer, GEMM on
+    its views."""
+    from gcnasm_b200.sharded import ColumnShardedGemm
+
+    m, n, k = 256, 384, 512
+    xb, xf = _bf16_input(O, (m, k), 28, scale=1.0)
+    qb, sfb = O.quant_128x128(O.fill_normal((n, k), 29, 1))
+    op = ColumnShardedGemm(T(qb), T(sfb), n)
+    out = op.forward_bf16(xb, m, k, DEV)
+    qa, sfa = O.quant_1x128(xf)
+    _, va, vs = op.activation_buffer(m, k, DEV)
+    assert np.array_equal(va.cpu().numpy(), qa) and np.array_equal(vs.cpu().numpy(), sfa)
+    assert_close(O, out.float().cpu().numpy(), O.gemm_ref_blockscale(qa, qb, sfa, sfb))

@@ -68,6 +68,23 @@ def _worker(rank, world, port, tmp):
     ok = np.array_equal(got, ref)
     shard = op(ta, tsfa, broadcast=False)
     ok = ok and np.array_equal(shard.numpy(), ref[:, n0:n1])
+    # bf16 activations: the root quantises into the single broadcast buffer, the others receive bytes + scales
+    xf = O.fill_normal((m, k), 3, 4)
+    xbits = O.f32_to_bf16_bits(xf)
+
+    def cpu_quant(x, q, tsfa):
+        qq, ss = O.quant_1x128(O.bf16_bits_to_f32(x.view(torch.int16).numpy().view(np.uint16)))
+        q.copy_(torch.from_numpy(qq))
+        tsfa.copy_(torch.from_numpy(ss))
+
+    op2 = ColumnShardedGemm(torch.from_numpy(b[n0:n1].copy()), torch.from_numpy(sfb[n0 // 128:n1 // 128].copy()), n,
+                            gemm_fn=cpu_gemm, out_dtype=torch.float32, quant_fn=cpu_quant)
+    xb = torch.from_numpy(xbits.view(np.int16).copy()).view(torch.bfloat16) if rank == 0 else None
+    shard2 = op2.forward_bf16(xb, m, k, "cpu", root=0)
+    qa, sa = O.quant_1x128(O.bf16_bits_to_f32(xbits))
+    ok = ok and np.array_equal(shard2.numpy(), O.gemm_ref_blockscale(qa, b, sa, sfb)[:, n0:n1])
+    _, va, vs = op2.activation_buffer(m, k, "cpu")
+    ok = ok and np.array_equal(va.numpy(), qa) and np.array_equal(vs.numpy(), sa)
     open(os.path.join(tmp, f"ok{rank}"), "w").write("1" if ok else "0")
     dist.barrier()
     dist.destroy_process_group()
