@@ -435,6 +435,27 @@ def main():
                      "frac_of_measured_hbm": qbytes / qus / 1e3 / measured_peaks()["hbm_gbs"]}
         del xb, aq, asf
 
+    # ---- in-repo HBM probe: read-only and read+write streams over 2 GiB ----
+    hbm_probe = None
+    if world == 1 and not args.no_decode:
+        pb = torch.empty(2 << 30, dtype=torch.uint8, device=dev).fill_(3)
+        pc = torch.empty_like(pb)
+        psum = torch.zeros(1, dtype=torch.int32, device=dev)
+        hbm_probe = {"bytes": pb.numel()}
+        for name, fn, moved in (("read_gbs", lambda: api.membw_read(pb, psum), 1), ("copy_gbs", lambda: api.membw_copy(pb, pc), 2)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record()
+            for _ in range(10):
+                fn()
+            p1.record()
+            torch.cuda.synchronize()
+            hbm_probe[name] = moved * pb.numel() / (p0.elapsed_time(p1) / 10) / 1e6
+        hbm_probe["measured_peaks_hbm_gbs"] = measured_peaks()["hbm_gbs"]
+        del pb, pc
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(args.workload)
@@ -451,7 +472,7 @@ def main():
                        "seed": SEED},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "kernel_ms": kern_ms, "device_status": status,
-            "decode": decode, "act_quant": act_quant,
+            "decode": decode, "act_quant": act_quant, "hbm_probe": hbm_probe,
         }
         print(json.dumps(line))
     if world > 1:

@@ -26,7 +26,7 @@ EXPORTS = (
     "b200_shuffle_b", "b200_unshuffle_b",
     "b200_cast_e4m3", "b200_quantize_tensor", "b200_quantize_tensor_workspace", "b200_quantize_1x128",
     "b200_quantize_128x128", "b200_quantize_mx32", "b200_mx_sf_relayout", "b200_mx_sf_bytes",
-    "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32",
+    "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32", "b200_membw_read", "b200_membw_copy",
     "b200_fill_uniform", "b200_fill_normal",
     "b200_last_status", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
     "b200_version", "b200_launch_count",
@@ -89,6 +89,8 @@ def lib() -> C.CDLL:
         "b200_quantize_mx32": (i32, [vp, vp, vp, i64, i64, vp]),
         "b200_quantize_act_bf16_1x128": (i32, [vp, i64, vp, i64, vp, i64, i64, i64, vp]),
         "b200_quantize_act_bf16_mx32": (i32, [vp, i64, vp, i64, vp, i64, i64, vp]),
+        "b200_membw_read": (i32, [vp, sz, vp, vp]),
+        "b200_membw_copy": (i32, [vp, vp, sz, vp]),
         "b200_mx_sf_relayout": (i32, [vp, vp, i64, i64, vp]),
         "b200_mx_sf_bytes": (sz, [i64, i64]),
         "b200_fill_uniform": (None, [vp, sz, u64, u32, f32, f32]),

@@ -11,6 +11,7 @@ import ctypes as C
 
 import numpy as np
 import torch
+from typing import Optional
 
 from . import _lib as L
 from ._lib import GemmArgs, check, lib
@@ -258,6 +259,26 @@ def quantize_act_bf16_mx32(x):
     check(lib().b200_quantize_act_bf16_mx32(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), atoms.data_ptr(), r, k,
                                             _stream()), "b200_quantize_act_bf16_mx32")
     return q, atoms
+
+
+# ---- HBM bandwidth probe ----------------------------------------------------------------------------
+def membw_read(buf: torch.Tensor, word_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Streams `buf` once (read only); returns a 1-element int32 tensor holding the sum of its 32-bit words
+    mod 2^32 (added to `word_sum` when given)."""
+    if word_sum is None:
+        word_sum = torch.zeros(1, dtype=torch.int32, device=buf.device)
+    check(lib().b200_membw_read(buf.data_ptr(), buf.numel() * buf.element_size(), word_sum.data_ptr(), _stream()),
+          "b200_membw_read")
+    return word_sum
+
+
+def membw_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """Streams `src` into `dst` (read + write)."""
+    nbytes = src.numel() * src.element_size()
+    if dst.numel() * dst.element_size() != nbytes:
+        raise ValueError("src and dst differ in size")
+    check(lib().b200_membw_copy(src.data_ptr(), dst.data_ptr(), nbytes, _stream()), "b200_membw_copy")
+    return dst
 
 
 # ---- seeded inputs (host) ---------------------------------------------------------------------------

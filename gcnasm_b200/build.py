@@ -56,7 +56,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_drivers(force: bool = False) -> list:
-    """The three C++ host drivers mirroring the reference's main() programs."""
+    """The C++ host drivers mirroring the reference's main() programs (three GEMM drivers and the bandwidth probe)."""
     os.makedirs(BIN, exist_ok=True)
     out = []
     if not os.path.isdir(DRIVERS):

@@ -186,6 +186,46 @@ __global__ void quant_1x128_kernel(const float* __restrict__ x, uint8_t* __restr
     if (lane == 0) sfa[g * M + row] = s;
 }
 
+// ---- HBM bandwidth probe ------------------------------------------------------------------------------------
+// Read-only and read+write streams over a buffer, the same two measurements as the reference's
+// bandwidth_memread/bandwidth_kernel.cu (memread_kernel :67-92, memcpy_kernel :94-118): persistent grid, 16-byte
+// accesses, eight loads in flight per thread, streaming cache hints.  The read kernel folds everything it loads
+// into a 32-bit word sum (so that the loads cannot be dropped, and so that a test can check every byte was read).
+__global__ void __launch_bounds__(1024) membw_read_kernel(const uint4* __restrict__ src, unsigned long long n16,
+                                                          unsigned int* __restrict__ word_sum) {
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    unsigned int acc = 0;
+    for (; i + 7 * stride < n16; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += v[j].x + v[j].y + v[j].z + v[j].w;
+    }
+    for (; i < n16; i += stride) {
+        const uint4 v = __ldcs(src + i);
+        acc += v.x + v.y + v.z + v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if ((threadIdx.x & 31) == 0 && acc != 0) atomicAdd(word_sum, acc);
+}
+
+__global__ void __launch_bounds__(1024) membw_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                          unsigned long long n16) {
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 7 * stride < n16; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) __stcs(dst + i + j * stride, v[j]);
+    }
+    for (; i < n16; i += stride) __stcs(dst + i, __ldcs(src + i));
+}
+
 // x / s, correctly rounded, for many x and one s.  With r = RN(1/s): q0 = RN(x*r), rem = x - q0*s (exact in an
 // FMA), q = RN(q0 + rem*r) is the correctly rounded quotient when nothing overflows or loses bits to underflow
 // (Markstein).  `fast` (uniform per group) says s is a normal number of moderate size; the callers guarantee

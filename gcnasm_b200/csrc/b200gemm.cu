@@ -886,6 +886,38 @@ int b200_quantize_1x128(const float* x, void* q, float* sfa, int64_t m, int64_t 
     g_launches.fetch_add(1);
     return B200_OK;
 }
+// persistent grid of the probe kernels: two 1024-thread blocks per SM, fewer for small buffers
+static unsigned membw_grid(int sm_count, unsigned long long n16) {
+    const unsigned long long want = (n16 + 1023) / 1024;
+    const unsigned long long cap = static_cast<unsigned long long>(sm_count) * 2;
+    return static_cast<unsigned>(want < cap ? (want ? want : 1) : cap);
+}
+int b200_membw_read(const void* src, size_t bytes, uint32_t* word_sum, void* stream) {
+    if (!src || !word_sum || bytes == 0) return B200_ERR_BAD_ARG;
+    if (bytes % 16 != 0 || !aligned16(src)) return B200_ERR_UNSUPPORTED;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    const unsigned long long n16 = bytes / 16;
+    membw_read_kernel<<<membw_grid(ds->sm_count, n16), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), n16, word_sum);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_membw_copy(const void* src, void* dst, size_t bytes, void* stream) {
+    if (!src || !dst || bytes == 0) return B200_ERR_BAD_ARG;
+    if (bytes % 16 != 0 || !aligned16(src) || !aligned16(dst)) return B200_ERR_UNSUPPORTED;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    const unsigned long long n16 = bytes / 16;
+    membw_copy_kernel<<<membw_grid(ds->sm_count, n16), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), n16);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
 int b200_quantize_act_bf16_1x128(const void* x_bf16, int64_t ldx, void* q, int64_t ldq, float* sfa, int64_t stride_sfa,
                                  int64_t m, int64_t k, void* stream) {
     if (!x_bf16 || !q || !sfa || m <= 0 || k <= 0) return B200_ERR_BAD_ARG;

@@ -146,6 +146,14 @@ int b200_quantize_act_bf16_mx32(const void* x_bf16, int64_t ldx, void* q, int64_
 int b200_mx_sf_relayout(const void* sf_logical, void* sf_atoms, int64_t rows, int64_t k, void* cuda_stream);
 size_t b200_mx_sf_bytes(int64_t rows, int64_t k);
 
+/* ---- HBM bandwidth probe ---------------------------------------------------------------------- */
+/* The two streams of the reference's bandwidth_memread/bandwidth_kernel.cu (memread_kernel :67-92,
+ * memcpy_kernel :94-118): read-only and read+write over a caller-owned buffer, persistent grid, 16-byte
+ * accesses.  bytes % 16 == 0, pointers 16-byte aligned.  The caller times the launches.
+ * read: adds the sum (mod 2^32) of all 32-bit words of the buffer to *word_sum (device memory, caller zeroes). */
+int b200_membw_read(const void* src, size_t bytes, uint32_t* word_sum, void* cuda_stream);
+int b200_membw_copy(const void* src, void* dst, size_t bytes, void* cuda_stream);
+
 /* ---- seeded inputs (host) --------------------------------------------------------------------- */
 /* The reference draws inputs from std::random_device (gemm_a8w8_8wave.cc:570-571), which cannot be
  * reproduced; these counter-based generators replace it.  Element i depends only on (seed, tensor_id, i). */
