@@ -19,6 +19,7 @@ OUT_F32, OUT_BF16 = 0, 1
 (TILE_AUTO, TILE_128x128, TILE_128x256, TILE_DECODE, TILE_PAIR_256x256, TILE_128x64, TILE_PAIR_256x128,
  TILE_PAIR_256x224, TILE_PAIR_256x192) = range(9)
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
+ERR_IO, ERR_CORRUPT = -7, -8
 
 # every symbol include/b200gemm.h declares
 EXPORTS = (
@@ -27,6 +28,7 @@ EXPORTS = (
     "b200_cast_e4m3", "b200_quantize_tensor", "b200_quantize_tensor_workspace", "b200_quantize_1x128",
     "b200_quantize_128x128", "b200_quantize_mx32", "b200_mx_sf_relayout", "b200_mx_sf_bytes",
     "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32", "b200_membw_read", "b200_membw_copy",
+    "b200_weight_file_write", "b200_weight_file_stat", "b200_weight_file_read",
     "b200_fill_uniform", "b200_fill_normal",
     "b200_last_status", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
     "b200_version", "b200_launch_count",
@@ -89,6 +91,9 @@ def lib() -> C.CDLL:
         "b200_quantize_mx32": (i32, [vp, vp, vp, i64, i64, vp]),
         "b200_quantize_act_bf16_1x128": (i32, [vp, i64, vp, i64, vp, i64, i64, i64, vp]),
         "b200_quantize_act_bf16_mx32": (i32, [vp, i64, vp, i64, vp, i64, i64, vp]),
+        "b200_weight_file_write": (i32, [C.c_char_p, i32, i32, i64, i64, vp, vp]),
+        "b200_weight_file_stat": (i32, [C.c_char_p, vp]),
+        "b200_weight_file_read": (i32, [C.c_char_p, vp, sz, vp, sz]),
         "b200_membw_read": (i32, [vp, sz, vp, vp]),
         "b200_membw_copy": (i32, [vp, vp, sz, vp]),
         "b200_mx_sf_relayout": (i32, [vp, vp, i64, i64, vp]),

@@ -17,6 +17,7 @@
 #include "decode_sm100.cuh"
 #include "gemm_pair_sm100.cuh"
 #include "gemm_sm100.cuh"
+#include "weight_file.h"
 
 namespace {
 
@@ -1036,6 +1037,14 @@ int b200_last_status(void) {
     return v;
 }
 int b200_last_cuda_error(void) { return g_last_cuda; }
+int b200_weight_file_write(const char* path, int32_t b_layout, int32_t scale_mode, int64_t n, int64_t k, const void* data,
+                           const void* scales) {
+    return b200::weight_file_write(path, b_layout, scale_mode, n, k, data, scales);
+}
+int b200_weight_file_stat(const char* path, b200_weight_desc* out) { return b200::weight_file_stat(path, out); }
+int b200_weight_file_read(const char* path, void* data, size_t data_capacity, void* scales, size_t scale_capacity) {
+    return b200::weight_file_read(path, data, data_capacity, scales, scale_capacity);
+}
 const char* b200_strerror(int code) {
     switch (code) {
         case B200_OK: return "ok";
@@ -1045,6 +1054,8 @@ const char* b200_strerror(int code) {
         case B200_ERR_DEVICE_TIMEOUT: return "bounded device wait expired";
         case B200_ERR_NO_DEVICE: return "no sm_100 device";
         case B200_ERR_TOO_LARGE: return "request exceeds an internal capacity";
+        case B200_ERR_IO: return "weight file i/o failed";
+        case B200_ERR_CORRUPT: return "weight file checksum mismatch";
         default: return "unknown";
     }
 }

@@ -48,6 +48,7 @@ struct Options {
     uint64_t seed = 1234;
     std::string scale = "";                        // none | tensor | block | mx (driver default if empty)
     std::string out = "f32";                       // f32 | bf16   (the reference writes fp32)
+    std::string save_weights = "", load_weights = "";  // flatmm: weight file written after / read instead of the shuffle
     std::string dist = "ref";                      // ref: A~U[0,1) B~U[-.5,.5) as the reference; u11: U[-1,1]; n01: N(0,1)
     int tile = 0;
     bool json = false;
@@ -89,6 +90,8 @@ inline Options parse(int argc, char** argv, int default_verify) {
         else if (take(argc, argv, i, nullptr, "--tile", v)) o.tile = std::atoi(v.c_str());
         else if (take(argc, argv, i, nullptr, "--warmup", v)) o.warmup = std::atoi(v.c_str());
         else if (take(argc, argv, i, nullptr, "--iters", v)) o.iters = std::atoi(v.c_str());
+        else if (take(argc, argv, i, nullptr, "--save-weights", v)) o.save_weights = v;
+        else if (take(argc, argv, i, nullptr, "--load-weights", v)) o.load_weights = v;
         else if (std::strcmp(argv[i], "--json") == 0) o.json = true;
     }
     return o;

@@ -6,9 +6,19 @@
 // shuffle; the launch at :780 is replaced by b200_gemm_a8w8().
 // Additions: --scale block applies the block-scale semantics of gemm_a8w8_blockscale to the flat layout
 // (per-token 1x128 A scales, 128x128 B scales) for decode shapes; --out bf16; --seed; --json.
+// --save-weights FILE writes the shuffled operand and its block scales after the shuffle; --load-weights FILE
+// starts from such a file instead of generating and shuffling B (batch 1), so that a decode run skips the
+// layout pass the reference repeats at every start (:736-742).
 #include "driver_common.h"
 
 using namespace drv;
+
+static void unshuffle_b_host(const uint8_t* flat, uint8_t* b_kn, int n, int k) {
+#pragma omp parallel for
+    for (int nn = 0; nn < n; ++nn)
+        for (int kk = 0; kk < k; ++kk)
+            b_kn[(size_t)kk * n + nn] = flat[(size_t)(nn / 16) * ((size_t)k * 16) + (size_t)(kk / 16) * 256 + (nn % 16) * 16 + (kk % 16)];
+}
 
 static void shuffle_b_host(const uint8_t* b_kn, uint8_t* out, int n, int k) {
 #pragma omp parallel for
@@ -57,9 +67,13 @@ int main(int argc, char** argv) {
     const bool bf16 = o.out == "bf16";
     const size_t M = o.m, N = o.n, K = o.k, B = o.batch, KG = K / 128, NG = N / 128;
 
+    const bool from_file = !o.load_weights.empty();
+    if ((from_file || !o.save_weights.empty()) && o.batch != 1) {
+        std::fprintf(stderr, "weight files hold one matrix: use -b 1.\n");
+        return 1;
+    }
     std::vector<uint8_t> ha(B * M * K), hb(B * N * K), hflat(B * N * K);
     fill_e4m3(ha.data(), ha.size(), o.seed, 0, o.dist, 0.0f, 1.0f);
-    fill_e4m3(hb.data(), hb.size(), o.seed, 1, o.dist, -0.5f, 0.5f);   // [K,N] per batch (:732)
     std::vector<float> hsfa, hsfb;
     if (block) {
         hsfa.resize(B * KG * M);
@@ -67,23 +81,44 @@ int main(int argc, char** argv) {
         b200_fill_uniform(hsfa.data(), hsfa.size(), o.seed, 2, 0.8f, 1.2f);
         b200_fill_uniform(hsfb.data(), hsfb.size(), o.seed, 3, 0.8f, 1.2f);
     }
-
     uint8_t* da = dev_upload(ha.data(), ha.size());
-    uint8_t* dkn = dev_upload(hb.data(), hb.size());
     uint8_t* dflat = nullptr;
-    DRV_CUDA(cudaMalloc(&dflat, hb.size()));
-    std::printf("Shuffling B matrix for FlatMM layout (batch=%d)...\n", o.batch);
-    for (size_t b = 0; b < B; ++b) DRV_B200(b200_shuffle_b(dkn + b * N * K, dflat + b * N * K, o.n, o.k, 1, nullptr));
-    DRV_CUDA(cudaMemcpy(hflat.data(), dflat, hflat.size(), cudaMemcpyDeviceToHost));
-    cudaFree(dkn);
     bool shuffle_ok = true;
-    if (o.verify) {
-        std::vector<uint8_t> want(N * K);
-        for (size_t b = 0; b < B; ++b) {
-            shuffle_b_host(hb.data() + b * N * K, want.data(), o.n, o.k);
-            shuffle_ok = shuffle_ok && std::memcmp(want.data(), hflat.data() + b * N * K, N * K) == 0;
+    if (from_file) {
+        b200_weight_desc wd;
+        DRV_B200(b200_weight_file_stat(o.load_weights.c_str(), &wd));
+        if (wd.n != o.n || wd.k != o.k || wd.b_layout != B200_B_FLAT_16x16 ||
+            wd.scale_mode != (block ? B200_SCALE_BLOCK : B200_SCALE_NONE)) {
+            std::fprintf(stderr, "%s holds N=%lld K=%lld layout %d scales %d: not what this run asks for.\n", o.load_weights.c_str(),
+                         (long long)wd.n, (long long)wd.k, wd.b_layout, wd.scale_mode);
+            return 1;
         }
-        std::printf("[shuffle_b] device vs host: %s\n", shuffle_ok ? "BIT-EXACT" : "MISMATCH");
+        DRV_B200(b200_weight_file_read(o.load_weights.c_str(), hflat.data(), hflat.size(), block ? hsfb.data() : nullptr,
+                                       block ? hsfb.size() * sizeof(float) : 0));
+        std::printf("Loaded pre-shuffled B from %s (checksum ok); no shuffle pass.\n", o.load_weights.c_str());
+        dflat = dev_upload(hflat.data(), hflat.size());
+        if (o.verify) unshuffle_b_host(hflat.data(), hb.data(), o.n, o.k);   // the host check reads the [K,N] matrix
+    } else {
+        fill_e4m3(hb.data(), hb.size(), o.seed, 1, o.dist, -0.5f, 0.5f);   // [K,N] per batch (:732)
+        uint8_t* dkn = dev_upload(hb.data(), hb.size());
+        DRV_CUDA(cudaMalloc(&dflat, hb.size()));
+        std::printf("Shuffling B matrix for FlatMM layout (batch=%d)...\n", o.batch);
+        for (size_t b = 0; b < B; ++b) DRV_B200(b200_shuffle_b(dkn + b * N * K, dflat + b * N * K, o.n, o.k, 1, nullptr));
+        DRV_CUDA(cudaMemcpy(hflat.data(), dflat, hflat.size(), cudaMemcpyDeviceToHost));
+        cudaFree(dkn);
+        if (o.verify) {
+            std::vector<uint8_t> want(N * K);
+            for (size_t b = 0; b < B; ++b) {
+                shuffle_b_host(hb.data() + b * N * K, want.data(), o.n, o.k);
+                shuffle_ok = shuffle_ok && std::memcmp(want.data(), hflat.data() + b * N * K, N * K) == 0;
+            }
+            std::printf("[shuffle_b] device vs host: %s\n", shuffle_ok ? "BIT-EXACT" : "MISMATCH");
+        }
+        if (!o.save_weights.empty()) {
+            DRV_B200(b200_weight_file_write(o.save_weights.c_str(), B200_B_FLAT_16x16, block ? B200_SCALE_BLOCK : B200_SCALE_NONE, o.n,
+                                            o.k, hflat.data(), block ? hsfb.data() : nullptr));
+            std::printf("Wrote %s\n", o.save_weights.c_str());
+        }
     }
     float *dsfa = nullptr, *dsfb = nullptr;
     if (block) {

@@ -42,7 +42,9 @@ enum b200_error {
     B200_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; b200_last_cuda_error() has the code */
     B200_ERR_DEVICE_TIMEOUT = -4,/* a bounded device-side wait expired (b200_last_status)                  */
     B200_ERR_NO_DEVICE = -5,     /* no sm_100 device / driver entry point unavailable                      */
-    B200_ERR_TOO_LARGE = -6      /* request exceeds a fixed internal capacity                              */
+    B200_ERR_TOO_LARGE = -6,     /* request exceeds a fixed internal capacity or a caller's buffer          */
+    B200_ERR_IO = -7,            /* weight file: cannot open / short read or write / truncated             */
+    B200_ERR_CORRUPT = -8        /* weight file: checksum mismatch                                         */
 };
 
 /* ---- GEMM arguments ---------------------------------------------------------------------- */
@@ -145,6 +147,29 @@ int b200_quantize_act_bf16_mx32(const void* x_bf16, int64_t ldx, void* q, int64_
  * [K/128][ceil(rows/128)][32][4][4] bytes, padded rows = 127 (scale 1.0).  Size: b200_mx_sf_bytes().     */
 int b200_mx_sf_relayout(const void* sf_logical, void* sf_atoms, int64_t rows, int64_t k, void* cuda_stream);
 size_t b200_mx_sf_bytes(int64_t rows, int64_t k);
+
+/* ---- weight files (host only) ------------------------------------------------------------------ */
+/* A pre-quantised, optionally pre-shuffled B operand with its scales on disk, so that a run does not repeat the
+ * host-side layout pass the reference performs at every start (opus_fmm/flatmm_a8w8_gfx950.cc:736-742).  The
+ * reference has no file format; this one is: 128-byte header below, N*K operand bytes, padding to 64, scales.
+ * Little-endian.  checksum = FNV-1a/64 over operand bytes then scale bytes.                                 */
+typedef struct b200_weight_desc {
+    char magic[8];            /* "B200WGT1" */
+    int32_t version;          /* 1 */
+    int32_t b_layout;         /* b200_b_layout of the operand bytes */
+    int32_t scale_mode;       /* b200_scale_mode: which scales follow */
+    int32_t reserved0;
+    int64_t n, k;
+    int64_t data_bytes;       /* n * k */
+    int64_t scale_bytes;      /* NONE 0; TENSOR 4; BLOCK 4*(n/128)*(k/128); MX b200_mx_sf_bytes(n, k) (atoms) */
+    uint64_t checksum;
+    uint8_t reserved[64];
+} b200_weight_desc;
+int b200_weight_file_write(const char* path, int32_t b_layout, int32_t scale_mode, int64_t n, int64_t k, const void* data,
+                           const void* scales);
+int b200_weight_file_stat(const char* path, b200_weight_desc* out);
+/* host buffers; B200_ERR_TOO_LARGE if a capacity is too small, B200_ERR_CORRUPT on a checksum mismatch */
+int b200_weight_file_read(const char* path, void* data, size_t data_capacity, void* scales, size_t scale_capacity);
 
 /* ---- HBM bandwidth probe ---------------------------------------------------------------------- */
 /* The two streams of the reference's bandwidth_memread/bandwidth_kernel.cu (memread_kernel :67-92,

@@ -59,3 +59,23 @@ def test_flatmm_driver(drivers):
     assert "Launching FlatMM kernel: M=256, N=512, K=256" in out and "ALL BATCHES VALID" in out
     out = run(drivers, "flatmm_a8w8", "-m", "16", "-n", "2304", "-k", "1024", "-b", "1", "--scale", "block", "--out", "bf16")
     assert "ALL BATCHES VALID" in out and "tile_config=3" in out
+
+
+def test_flatmm_weight_file_round_trip(drivers, tmp_path):
+    """--save-weights after the shuffle, then --load-weights instead of it: same self-check, no shuffle pass; the
+    file is the reference's flat image plus the block scales."""
+    from gcnasm_b200 import _lib as L
+    from gcnasm_b200 import weights
+
+    wfile = str(tmp_path / "decode.b2w")
+    shape = ["-m", "16", "-n", "1024", "-k", "1024", "-b", "1", "--scale", "block", "--out", "bf16"]
+    out = run(drivers, "flatmm_a8w8", *shape, "--save-weights", wfile)
+    assert "BIT-EXACT" in out and "ALL BATCHES VALID" in out and f"Wrote {wfile}" in out
+    info = weights.stat(wfile)
+    assert (info.n, info.k, info.b_layout, info.scale_mode) == (1024, 1024, L.B_FLAT_16x16, L.SCALE_BLOCK)
+    out = run(drivers, "flatmm_a8w8", *shape, "--load-weights", wfile)
+    assert "no shuffle pass" in out and "Shuffling B" not in out and "ALL BATCHES VALID" in out and "FAIL" not in out
+    # a file for another shape is refused
+    bad = subprocess.run([os.path.join(drivers, "flatmm_a8w8"), "-m", "16", "-n", "2048", "-k", "1024", "-b", "1", "--scale", "block",
+                          "--load-weights", wfile], capture_output=True, text=True)
+    assert bad.returncode == 1 and "not what this run asks for" in bad.stderr
