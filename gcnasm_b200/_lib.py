@@ -24,7 +24,8 @@ ERR_IO, ERR_CORRUPT = -7, -8
 # every symbol include/b200gemm.h declares
 EXPORTS = (
     "b200_gemm_a8w8", "b200_gemm_check", "b200_gemm_a8w8_simple", "b200_gemm_a8w8_host", "b200_gemm_a8w8_decode_static",
-    "b200_shuffle_b", "b200_unshuffle_b",
+    "b200_shuffle_b", "b200_unshuffle_b", "b200_gemm_a16w16", "b200_gemm_a16w16_check", "b200_shuffle_b_bf16",
+    "b200_unshuffle_b_bf16",
     "b200_cast_e4m3", "b200_quantize_tensor", "b200_quantize_tensor_workspace", "b200_quantize_1x128",
     "b200_quantize_128x128", "b200_quantize_mx32", "b200_mx_sf_relayout", "b200_mx_sf_bytes",
     "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32", "b200_membw_read", "b200_membw_copy",
@@ -81,6 +82,10 @@ def lib() -> C.CDLL:
         "b200_gemm_a8w8_simple": (i32, [P, vp]),
         "b200_gemm_a8w8_host": (i32, [P, vp]),
         "b200_gemm_a8w8_decode_static": (i32, [P, vp]),
+        "b200_gemm_a16w16": (i32, [P, vp]),
+        "b200_gemm_a16w16_check": (i32, [P, C.POINTER(C.c_int32)]),
+        "b200_shuffle_b_bf16": (i32, [vp, vp, i64, i64, i32, vp]),
+        "b200_unshuffle_b_bf16": (i32, [vp, vp, i64, i64, i32, vp]),
         "b200_shuffle_b": (i32, [vp, vp, i64, i64, i32, vp]),
         "b200_unshuffle_b": (i32, [vp, vp, i64, i64, i32, vp]),
         "b200_cast_e4m3": (i32, [vp, vp, i64, vp]),

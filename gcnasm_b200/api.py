@@ -261,6 +261,82 @@ def quantize_act_bf16_mx32(x):
     return q, atoms
 
 
+# ---- a16w16 siblings (bf16 operands) ----------------------------------------------------------------
+def gemm_a16w16(a, b, scale_a=None, scale_b=None, *, n=None, flat=False, out=None, out_dtype=torch.bfloat16,
+                tile=L.TILE_AUTO):
+    """``C = A @ B^T`` on bf16 operands, fp32 accumulate (``opus_gemm/gemm_a16w16_8wave.cc``).  ``a`` is
+    ``[M, K]`` or ``[batch, M, K]`` bf16; ``b`` is ``[N, K]`` / ``[batch, N, K]`` bf16, or with ``flat=True`` the
+    image made by :func:`shuffle_b_bf16` (then ``n=`` is required)."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("A and B must be torch.bfloat16")
+    squeeze = a.dim() == 2
+    if squeeze:
+        a = a.unsqueeze(0)
+    batch, m, k = a.shape
+    if a.stride(2) != 1:
+        raise ValueError("A must be K-contiguous")
+    if not flat:
+        if b.dim() == 2:
+            b = b.unsqueeze(0)
+        if b.shape[0] != batch or b.shape[2] != k or b.stride(2) != 1:
+            raise ValueError("B must be [batch, N, K], K-contiguous, matching A")
+        n = b.shape[1]
+        stride_b, stride_b_batch = b.stride(1), b.stride(0)
+    else:
+        if n is None:
+            raise ValueError("flat B needs n=")
+        if not b.is_contiguous() or b.numel() != batch * n * k:
+            raise ValueError("flat B must be a contiguous image of batch*N*K values")
+        stride_b, stride_b_batch = n, n * k
+    if out is None:
+        out = torch.empty((batch, m, n), dtype=out_dtype, device=a.device)
+    else:
+        if out.dim() == 2:
+            out = out.unsqueeze(0)
+        if out.shape != (batch, m, n) or out.stride(2) != 1:
+            raise ValueError("out must be [batch, M, N], N-contiguous")
+    args = GemmArgs()
+    args.ptr_a, args.ptr_b, args.ptr_c = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k, args.batch = m, n, k, batch
+    args.stride_a, args.stride_b, args.stride_c = a.stride(1), stride_b, out.stride(1)
+    args.stride_a_batch, args.stride_b_batch, args.stride_c_batch = a.stride(0), stride_b_batch, out.stride(0)
+    keep = [a, b, out]
+    mode = L.SCALE_NONE
+    if scale_a is not None or scale_b is not None:
+        mode = L.SCALE_TENSOR
+        for name, sc in (("ptr_scale_a", scale_a), ("ptr_scale_b", scale_b)):
+            if sc is not None:
+                if sc.dtype != torch.float32 or not sc.is_cuda or sc.numel() != 1:
+                    raise TypeError("per-tensor scales are 1-element float32 CUDA tensors")
+                setattr(args, name, sc.data_ptr())
+                keep.append(sc)
+    args.scale_mode, args.b_layout = mode, (L.B_FLAT_16x16 if flat else L.B_NK_ROWMAJOR)
+    args.out_dtype, args.tile_hint = _out_code(out.dtype), tile
+    check(lib().b200_gemm_a16w16(C.byref(args), _stream()), "b200_gemm_a16w16")
+    return out[0] if squeeze else out
+
+
+def shuffle_b_bf16(b: torch.Tensor, src: str = "kn") -> torch.Tensor:
+    """bf16 weights ``[K, N]`` (``src='kn'``, what the reference's shuffle_b takes) or ``[N, K]`` -> flat
+    ``[N/16][K/8][16][8]`` (``opus_fmm/flatmm_a16w16_gfx950.cc:623-666``)."""
+    if b.dtype != torch.bfloat16 or not b.is_contiguous() or b.dim() != 2:
+        raise ValueError("B must be a contiguous 2-D bf16 tensor")
+    k, n = (b.shape if src == "kn" else (b.shape[1], b.shape[0]))
+    out = torch.empty(n * k, dtype=torch.bfloat16, device=b.device)
+    check(lib().b200_shuffle_b_bf16(b.data_ptr(), out.data_ptr(), n, k, 1 if src == "kn" else 0, _stream()),
+          "b200_shuffle_b_bf16")
+    return out
+
+
+def unshuffle_b_bf16(flat: torch.Tensor, n: int, k: int, dst: str = "kn") -> torch.Tensor:
+    if flat.dtype != torch.bfloat16 or not flat.is_contiguous() or flat.numel() != n * k:
+        raise ValueError("flat B must be a contiguous bf16 image of N*K values")
+    out = torch.empty((k, n) if dst == "kn" else (n, k), dtype=torch.bfloat16, device=flat.device)
+    check(lib().b200_unshuffle_b_bf16(flat.data_ptr(), out.data_ptr(), n, k, 1 if dst == "kn" else 0, _stream()),
+          "b200_unshuffle_b_bf16")
+    return out
+
+
 # ---- HBM bandwidth probe ----------------------------------------------------------------------------
 def membw_read(buf: torch.Tensor, word_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Streams `buf` once (read only); returns a 1-element int32 tensor holding the sum of its 32-bit words

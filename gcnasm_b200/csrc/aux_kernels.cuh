@@ -116,6 +116,65 @@ __global__ void shuffle_kn_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     }
 }
 
+// ---- 16-bit elements, [K][N] row-major <-> flat [N/16][K/8][16 n][8 k] (16-byte items of 8 values, the reference's
+// shuffle_b for bf16: opus_fmm/flatmm_a16w16_gfx950.cc:623-666).  In bytes the flat image has the geometry of the
+// 8-bit one over a [N][2K]-byte matrix.  A 64(K) x 64(N) element tile goes through shared memory.
+template <bool kToFlat>
+__global__ void shuffle_kn16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, long long N, long long K) {
+    __shared__ __align__(16) uint16_t tile[64][64 + 8];
+    const long long n0 = static_cast<long long>(blockIdx.x) * 64;
+    const long long k0 = static_cast<long long>(blockIdx.y) * 64;
+    const int t = threadIdx.x;                                       // 256 threads
+    // flat item (n, k8): element offset (n/16)*(K*16) + (k8)*128 + (n%16)*8
+    if (kToFlat) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {                                // 64 rows x 8 uint4 (8 values each)
+            const int kk = i * 32 + (t >> 3);
+            const int nn = (t & 7) * 8;
+            if (k0 + kk < K && n0 + nn < N)
+                *reinterpret_cast<uint4*>(&tile[kk][nn]) = __ldg(reinterpret_cast<const uint4*>(src + (k0 + kk) * N + n0 + nn));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {                                // 64 n x 8 k-chunks = 512 items
+            const int item = i * 256 + t;
+            const int c = item >> 6, nn = item & 63;
+            if (n0 + nn < N && k0 + c * 8 < K) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    w[q] = static_cast<uint32_t>(tile[c * 8 + 2 * q][nn]) | (static_cast<uint32_t>(tile[c * 8 + 2 * q + 1][nn]) << 16);
+                const long long n = n0 + nn, k8 = (k0 >> 3) + c;
+                *reinterpret_cast<uint4*>(dst + (n >> 4) * (K * 16) + k8 * 128 + (n & 15) * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int item = i * 256 + t;
+            const int c = item >> 6, nn = item & 63;
+            if (n0 + nn < N && k0 + c * 8 < K) {
+                const long long n = n0 + nn, k8 = (k0 >> 3) + c;
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (n >> 4) * (K * 16) + k8 * 128 + (n & 15) * 8));
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    tile[c * 8 + 2 * q][nn] = static_cast<uint16_t>(w[q]);
+                    tile[c * 8 + 2 * q + 1][nn] = static_cast<uint16_t>(w[q] >> 16);
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int kk = i * 32 + (t >> 3);
+            const int nn = (t & 7) * 8;
+            if (k0 + kk < K && n0 + nn < N)
+                *reinterpret_cast<uint4*>(dst + (k0 + kk) * N + n0 + nn) = *reinterpret_cast<const uint4*>(&tile[kk][nn]);
+        }
+    }
+}
+
 // ---- quantisers ----------------------------------------------------------------------------------
 __global__ void cast_e4m3_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, long long count) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;

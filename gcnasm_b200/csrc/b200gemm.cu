@@ -193,7 +193,8 @@ struct Plan {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
+// ab16: `a` is the byte view of a bf16 problem (K and the A/B strides counted in bytes)
+int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = false) {
     if (!a || !a->ptr_a || !a->ptr_b || !a->ptr_c) return B200_ERR_BAD_ARG;
     if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return B200_ERR_BAD_ARG;
     if (a->scale_mode < 0 || a->scale_mode > 3 || a->b_layout < 0 || a->b_layout > 1 || a->out_dtype < 0 ||
@@ -224,9 +225,10 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
         if (a->batch > 1 && (a->stride_sfa_batch % 16 != 0 || a->stride_sfb_batch % 16 != 0)) return B200_ERR_UNSUPPORTED;
     }
 
+    if (ab16 && (a->scale_mode == B200_SCALE_BLOCK || a->scale_mode == B200_SCALE_MX)) return B200_ERR_UNSUPPORTED;
     Plan pl{B200_TILE_128x128, 0, 1};
     const int64_t kblocks = (a->k + 127) / 128;
-    const bool decode_ok = a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
+    const bool decode_ok = !ab16 && a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
     int hint = a->tile_hint;
     if (hint == B200_TILE_DECODE && !decode_ok) return B200_ERR_UNSUPPORTED;
     if (hint == B200_TILE_128x64) return B200_ERR_UNSUPPORTED;
@@ -262,6 +264,8 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
             } else {
                 if (a->m > 128) {
                     consider(B200_TILE_PAIR_256x256, 256, true);
+                }
+                if (a->m > 128 && !ab16) {
                     consider(B200_TILE_PAIR_256x224, 224, true);
                     consider(B200_TILE_PAIR_256x192, 192, true);
                     consider(B200_TILE_PAIR_256x128, 128, true);
@@ -272,6 +276,8 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan) {
         }
     }
     if (mx && !(hint == B200_TILE_128x128 || (hint == B200_TILE_PAIR_256x256 && mx_pair_ok))) return B200_ERR_UNSUPPORTED;
+    // bf16 operands: pair 256x256 and the two single-CTA tiles are built
+    if (ab16 && !(hint == B200_TILE_128x128 || hint == B200_TILE_128x256 || hint == B200_TILE_PAIR_256x256)) return B200_ERR_UNSUPPORTED;
     pl.tile = hint;
     if (hint == B200_TILE_DECODE) {
         pl.mt = a->m <= 16 ? 16 : (a->m <= 32 ? 32 : 64);
@@ -570,7 +576,7 @@ int run_decode_static(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, 
     return B200_OK;
 }
 
-int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
+int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st, bool ab16 = false) {
     int BN = 128;
     bool pair = false;
     switch (pl.tile) {
@@ -643,6 +649,13 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         p.sfa_batch = a->stride_sfa_batch;
         p.sfb_batch = a->stride_sfb_batch;
     }
+    if (ab16) {
+        const bool flat16 = a->b_layout == B200_B_FLAT_16x16;
+        if (pair) return flat16 ? launch_pair<256, MODE_ACC16, BL_FLAT>(p, ds->sm_count, st) : launch_pair<256, MODE_ACC16, BL_NK>(p, ds->sm_count, st);
+        const int grid16 = p.tiles_total < ds->sm_count ? p.tiles_total : ds->sm_count;
+        if (BN == 256) return flat16 ? launch_gemm<256, MODE_ACC16, BL_FLAT>(p, grid16, st) : launch_gemm<256, MODE_ACC16, BL_NK>(p, grid16, st);
+        return flat16 ? launch_gemm<128, MODE_ACC16, BL_FLAT>(p, grid16, st) : launch_gemm<128, MODE_ACC16, BL_NK>(p, grid16, st);
+    }
     if (pair) {
         switch (BN) {
             case 256: return launch_pair_modes<256>(a, p, ds->sm_count, st);
@@ -713,6 +726,43 @@ int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream) {
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     if (pl.tile == B200_TILE_DECODE) return run_decode(args, pl, ds, st);
     return run_gemm(args, pl, ds, st);
+}
+
+// bf16 operands: the same pipeline on the byte view of the problem (a bf16 row of K elements is a row of 2K bytes;
+// tile bytes, swizzle and descriptor steps are those of the 8-bit path), with kind::f16 MMAs
+static int byte_view16(const b200_gemm_args* a, b200_gemm_args* v) {
+    if (!a) return B200_ERR_BAD_ARG;
+    if (a->k > 0x3FFFFFFF) return B200_ERR_TOO_LARGE;
+    *v = *a;
+    v->k = a->k * 2;
+    v->stride_a = a->stride_a * 2;
+    v->stride_b = a->stride_b * 2;
+    v->stride_a_batch = a->stride_a_batch * 2;
+    v->stride_b_batch = a->stride_b_batch * 2;
+    return B200_OK;
+}
+int b200_gemm_a16w16_check(const b200_gemm_args* args, int32_t* chosen_tile) {
+    b200_gemm_args v;
+    int rc = byte_view16(args, &v);
+    if (rc) return rc;
+    Plan pl;
+    rc = validate(&v, 148, &pl, true);
+    if (rc == B200_OK && chosen_tile) *chosen_tile = pl.tile;
+    return rc;
+}
+int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream) {
+    b200_gemm_args v;
+    int rc = byte_view16(args, &v);
+    if (rc) return rc;
+    Plan pl;
+    rc = validate(&v, 148, &pl, true);
+    if (rc) return rc;
+    DeviceState* ds = nullptr;
+    rc = device_state(&ds);
+    if (rc) return rc;
+    rc = validate(&v, ds->sm_count, &pl, true);
+    if (rc) return rc;
+    return run_gemm(&v, pl, ds, static_cast<cudaStream_t>(cuda_stream), true);
 }
 
 int b200_gemm_a8w8_decode_static(const b200_gemm_args* args, void* cuda_stream) {
@@ -845,6 +895,27 @@ int b200_shuffle_b(const void* src, void* dst, int64_t n, int64_t k, int32_t src
 }
 int b200_unshuffle_b(const void* flat, void* dst, int64_t n, int64_t k, int32_t dst_is_kn, void* stream) {
     return shuffle_common(flat, dst, n, k, dst_is_kn, false, stream);
+}
+
+static int shuffle16_common(const void* src, void* dst, int64_t n, int64_t k, int32_t kn, bool to_flat, void* stream) {
+    if (!src || !dst || n <= 0 || k <= 0) return B200_ERR_BAD_ARG;
+    if (n % 16 != 0 || k % 8 != 0) return B200_ERR_UNSUPPORTED;
+    if (!kn) return shuffle_common(src, dst, n, 2 * k, 0, to_flat, stream);      // [N][K] bf16 = [N][2K] bytes
+    if (!aligned16(src) || !aligned16(dst)) return B200_ERR_UNSUPPORTED;
+    dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((k + 63) / 64));
+    if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (to_flat) shuffle_kn16_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), n, k);
+    else shuffle_kn16_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), n, k);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
+int b200_shuffle_b_bf16(const void* src, void* dst, int64_t n, int64_t k, int32_t src_is_kn, void* stream) {
+    return shuffle16_common(src, dst, n, k, src_is_kn, true, stream);
+}
+int b200_unshuffle_b_bf16(const void* flat, void* dst, int64_t n, int64_t k, int32_t dst_is_kn, void* stream) {
+    return shuffle16_common(flat, dst, n, k, dst_is_kn, false, stream);
 }
 
 // ---- quantisers ------------------------------------------------------------------------------------

@@ -23,7 +23,8 @@ namespace b200 {
 // same results but measured 1475 against 2010 TFLOP/s on 8192^3 block-scale, so it is not built.
 template <int BN_, int MODE_, int BLAYOUT_, int EW_ = 8>
 struct PairCfg {
-    static constexpr int BM = 128, BN = BN_, BK = 128, MODE = MODE_, BLAYOUT = BLAYOUT_;
+    static constexpr bool AB16 = MODE_ == MODE_ACC16;               // bf16 operands: same bytes, kind::f16 MMAs
+    static constexpr int BM = 128, BN = BN_, BK = 128, MODE = AB16 ? MODE_ACC : MODE_, BLAYOUT = BLAYOUT_;
     static constexpr int EPI_WARPS = EW_, NSPLIT = EW_ / 4;         // column parts per row quadrant
     static constexpr int BH = BN / 2;                               // B rows loaded by each CTA
     static constexpr int A_BYTES = BM * BK;
@@ -283,7 +284,8 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                 const uint32_t tsf = tmem_base + Cfg::ACC_COLS;
                                 umma_mxf8<2>(tacc, da, db, make_idesc_mxf8(2 * BM, BN, k, k), accum, tsf, tsf + 4);
                             } else {
-                                umma_f8<2>(tacc, da, db, idesc, accum);
+                                if constexpr (Cfg::AB16) umma_f16<2>(tacc, da, db, make_idesc_bf16(2 * BM, BN), accum);
+                                else umma_f8<2>(tacc, da, db, idesc, accum);
                             }
                         }
                         B200_TRACE_MMA(4);

@@ -20,7 +20,8 @@
 
 namespace b200 {
 
-enum : int { MODE_ACC = 0, MODE_BLOCK = 1, MODE_MX = 2 };
+// MODE_ACC16: the accumulate-mode pipeline on bf16 operands (every K quantity counted in bytes by the launcher)
+enum : int { MODE_ACC = 0, MODE_BLOCK = 1, MODE_MX = 2, MODE_ACC16 = 3 };
 enum : int { BL_NK = 0, BL_FLAT = 1 };
 enum : int { OUT_F32 = 0, OUT_BF16 = 1 };
 
@@ -46,7 +47,8 @@ struct GemmParams {
 
 template <int BN_, int MODE_, int BLAYOUT_>
 struct GemmCfg {
-    static constexpr int BM = 128, BN = BN_, BK = 128, MODE = MODE_, BLAYOUT = BLAYOUT_;
+    static constexpr bool AB16 = MODE_ == MODE_ACC16;               // bf16 operands: same bytes, kind::f16 MMAs
+    static constexpr int BM = 128, BN = BN_, BK = 128, MODE = AB16 ? MODE_ACC : MODE_, BLAYOUT = BLAYOUT_;
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BN * BK;
     static constexpr int SFA_BYTES = (MODE == MODE_MX) ? 512 : 0;
@@ -302,7 +304,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_a8w8_sm100_kernel(const 
                                 const uint32_t tsf = tmem_base + Cfg::ACC_COLS;
                                 umma_mxf8<1>(tacc, da, db, make_idesc_mxf8(BM, BN, k, k), accum, tsf, tsf + 4);
                             } else {
-                                umma_f8<1>(tacc, da, db, idesc, accum);
+                                if constexpr (Cfg::AB16) umma_f16<1>(tacc, da, db, make_idesc_bf16(BM, BN), accum);
+                                else umma_f8<1>(tacc, da, db, idesc, accum);
                             }
                         }
                         umma_commit<1>(bar_empty0 + s * 8);      // stage free once these MMAs retire

@@ -113,6 +113,19 @@ int b200_gemm_a8w8_host(const b200_gemm_args* host_args, void* cuda_stream);
  *     different streams, or the same stream from different threads without ordering -- race on it.            */
 int b200_gemm_a8w8_decode_static(const b200_gemm_args* args, void* cuda_stream);
 
+/* ---- a16w16 siblings: bf16 operands -------------------------------------------------------------- */
+/* Replaces the launches of opus_gemm/gemm_a16w16_8wave.cc (kernel :252-560, launch in main) and
+ * opus_fmm/flatmm_a16w16_gfx950.cc (flat B): C = A * B^T with bf16 A [M][K] and B [N][K] (or the flat image of
+ * b200_shuffle_b_bf16), fp32 accumulate, bf16 (what the reference writes) or fp32 output.  Same b200_gemm_args;
+ * k and the A/B strides count bf16 ELEMENTS.  scale_mode NONE or TENSOR.  K % 8 == 0 (flat: K % 64 == 0, N % 16 == 0),
+ * stride_a, stride_b multiples of 8, 16-byte aligned bases.  Tiles: AUTO, 128x128, 128x256, PAIR_256x256.       */
+int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream);
+int b200_gemm_a16w16_check(const b200_gemm_args* args, int32_t* chosen_tile);
+/* shuffle_b<bf16> of opus_fmm/flatmm_a16w16_gfx950.cc:623-666 (ItemsPerAccess 8): [K][N] (src_is_kn != 0) or
+ * [N][K] row-major bf16 -> flat [N/16][K/8][16 n][8 k]; N % 16 == 0, K % 8 == 0.  Byte-exact.                     */
+int b200_shuffle_b_bf16(const void* src, void* dst, int64_t n, int64_t k, int32_t src_is_kn, void* cuda_stream);
+int b200_unshuffle_b_bf16(const void* flat, void* dst, int64_t n, int64_t k, int32_t dst_is_kn, void* cuda_stream);
+
 /* ---- weight pre-shuffle -------------------------------------------------------------------- */
 /* shuffle_b (flatmm_a8w8_gfx950.cc:638-681) on the device: src is [K][N] row-major when src_is_kn != 0
  * (the reference's input) or [N][K] row-major otherwise; dst is [N/16][K/16][16][16].  Bit-exact byte

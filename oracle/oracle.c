@@ -406,6 +406,67 @@ int orc_shuffle_b_nk(const uint8_t *b_nk, uint8_t *out, int N, int K) {
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* a16w16 siblings (bf16 operands)                                                       */
+/* ------------------------------------------------------------------------------------ */
+
+/* gemm_ref of opus_gemm/gemm_a16w16_8wave.cc:584-595: both operands widened to float, sequential fp32 sum over p,
+ * result rounded to bf16 (`static_cast<bf16_t>(sum)`, RNE).  out_bf16 == 0 keeps the fp32 sum.                    */
+void orc_gemm_ref_nt_bf16(const uint16_t *a, const uint16_t *b, void *c, int m, int n, int k, int64_t lda,
+                          int64_t ldb, int64_t ldc, int out_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int i = 0; i < m; ++i) {
+        for (int j = 0; j < n; ++j) {
+            float sum = 0.0f;
+            for (int p = 0; p < k; ++p) sum += orc_bf16_to_f32(a[i * lda + p]) * orc_bf16_to_f32(b[j * ldb + p]);
+            store_out(c, i * ldc + j, sum, out_bf16);
+        }
+    }
+}
+
+/* gemm_ref of opus_fmm/flatmm_a16w16_gfx950.cc:571-582: B is the UNSHUFFLED [K,N] matrix, b[p*ldb + j].            */
+void orc_gemm_ref_kn_bf16(const uint16_t *a, const uint16_t *b_kn, void *c, int m, int n, int k, int64_t lda,
+                          int64_t ldb, int64_t ldc, int out_bf16) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int i = 0; i < m; ++i) {
+        for (int j = 0; j < n; ++j) {
+            float sum = 0.0f;
+            for (int p = 0; p < k; ++p) sum += orc_bf16_to_f32(a[i * lda + p]) * orc_bf16_to_f32(b_kn[p * ldb + j]);
+            store_out(c, i * ldc + j, sum, out_bf16);
+        }
+    }
+}
+
+/* shuffle_b<bf16> of opus_fmm/flatmm_a16w16_gfx950.cc:623-666: ItemsPerAccess = min(16/sizeof(bf16), K_Warp_Tile/KLane)
+ * = 8 for the shipped traits (:627-629), N_Warp_Tile = 16; out[d0][d2][d1][d3] = in[(d2*8+d3)*N + d0*16+d1] with
+ * d0 = n/16, d1 = n%16, d2 = k/8, d3 = k%8.  Needs N % 16 == 0 and K % 8 == 0 (:631-633).                          */
+int orc_shuffle_b_bf16(const uint16_t *b_kn, uint16_t *out, int N, int K) {
+    if (N % 16 != 0 || K % 8 != 0) return -1;
+    const int dim0 = N / 16, dim2 = K / 8;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int d0 = 0; d0 < dim0; ++d0) {
+        for (int d2 = 0; d2 < dim2; ++d2) {
+            for (int d1 = 0; d1 < 16; ++d1) {
+                const uint16_t *src = b_kn + (size_t)(d2 * 8) * N + (d0 * 16 + d1);
+                uint16_t *dst = out + (size_t)d0 * ((size_t)dim2 * 128) + (size_t)d2 * 128 + d1 * 8;
+                for (int d3 = 0; d3 < 8; ++d3) dst[d3] = src[(size_t)d3 * N];
+            }
+        }
+    }
+    return 0;
+}
+
+int orc_unshuffle_b_bf16(const uint16_t *flat, uint16_t *b_kn, int N, int K) {
+    if (N % 16 != 0 || K % 8 != 0) return -1;
+    const int dim2 = K / 8;
+#pragma omp parallel for schedule(static)
+    for (int kk = 0; kk < K; ++kk)
+        for (int nn = 0; nn < N; ++nn)
+            b_kn[(size_t)kk * N + nn] = flat[(size_t)(nn / 16) * ((size_t)dim2 * 128) + (size_t)(kk / 8) * 128 +
+                                             (size_t)(nn % 16) * 8 + (kk % 8)];
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* checker                                                                               */
 /* ------------------------------------------------------------------------------------ */
 

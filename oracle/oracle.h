@@ -77,6 +77,15 @@ int orc_unshuffle_b(const uint8_t *flat, uint8_t *b_kn, int N, int K);
 /* [N,K] row-major -> the same flat layout */
 int orc_shuffle_b_nk(const uint8_t *b_nk, uint8_t *out, int N, int K);
 
+/* ---- a16w16 siblings: bf16 operands as uint16_t bit patterns ------------------------------ */
+void orc_gemm_ref_nt_bf16(const uint16_t *a, const uint16_t *b, void *c, int m, int n, int k, int64_t lda,
+                          int64_t ldb, int64_t ldc, int out_bf16);
+void orc_gemm_ref_kn_bf16(const uint16_t *a, const uint16_t *b_kn, void *c, int m, int n, int k, int64_t lda,
+                          int64_t ldb, int64_t ldc, int out_bf16);
+/* [K,N] row-major -> flat [N/16][K/8][16 n][8 k] */
+int orc_shuffle_b_bf16(const uint16_t *b_kn, uint16_t *out, int N, int K);
+int orc_unshuffle_b_bf16(const uint16_t *flat, uint16_t *b_kn, int N, int K);
+
 /* ---- checker ------------------------------------------------------------------------ */
 /* returns 1 when no |ref-res| exceeds threshold; prints up to 10 offenders if verbose   */
 int orc_valid_vector(const float *ref, const float *res, int64_t n, float threshold, int verbose);

@@ -53,6 +53,11 @@ def lib() -> C.CDLL:
         L.orc_gemm_ref_blockscale_rows.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i32]
         L.orc_gemm_ref_kn.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32]
         L.orc_gemm_ref_mx.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32]
+        L.orc_gemm_ref_nt_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32]
+        L.orc_gemm_ref_kn_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32]
+        for name in ("orc_shuffle_b_bf16", "orc_unshuffle_b_bf16"):
+            getattr(L, name).argtypes = [vp, vp, i32, i32]
+            getattr(L, name).restype = i32
         for name in ("orc_shuffle_b", "orc_unshuffle_b", "orc_shuffle_b_nk"):
             getattr(L, name).argtypes = [vp, vp, i32, i32]
             getattr(L, name).restype = i32
@@ -215,6 +220,38 @@ def shuffle_b_nk(b_nk: np.ndarray) -> np.ndarray:
     out = np.empty(N * K, np.uint8)
     if lib().orc_shuffle_b_nk(_p(b_nk), _p(out), N, K) != 0:
         raise ValueError("shuffle_b needs N % 16 == 0 and K % 16 == 0")
+    return out
+
+
+# ---- a16w16 siblings (bf16 bit patterns as uint16) ----------------------------------------------
+def gemm_ref_nt_bf16(a_bits, b_bits, out_bf16=True):
+    m, k = a_bits.shape
+    n = b_bits.shape[0]
+    c = _out(m, n, out_bf16)
+    lib().orc_gemm_ref_nt_bf16(_p(a_bits), _p(b_bits), _p(c), m, n, k, k, k, n, int(out_bf16))
+    return c
+
+
+def gemm_ref_kn_bf16(a_bits, b_kn_bits, out_bf16=True):
+    m, k = a_bits.shape
+    n = b_kn_bits.shape[1]
+    c = _out(m, n, out_bf16)
+    lib().orc_gemm_ref_kn_bf16(_p(a_bits), _p(b_kn_bits), _p(c), m, n, k, k, n, n, int(out_bf16))
+    return c
+
+
+def shuffle_b_bf16(b_kn_bits: np.ndarray) -> np.ndarray:
+    K, N = b_kn_bits.shape
+    out = np.empty(N * K, np.uint16)
+    if lib().orc_shuffle_b_bf16(_p(b_kn_bits), _p(out), N, K) != 0:
+        raise ValueError("bf16 shuffle_b needs N % 16 == 0 and K % 8 == 0")
+    return out
+
+
+def unshuffle_b_bf16(flat: np.ndarray, N: int, K: int) -> np.ndarray:
+    out = np.empty((K, N), np.uint16)
+    if lib().orc_unshuffle_b_bf16(_p(flat), _p(out), N, K) != 0:
+        raise ValueError("bf16 unshuffle_b needs N % 16 == 0 and K % 8 == 0")
     return out
 
 

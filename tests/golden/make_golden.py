@@ -158,6 +158,19 @@ def main():
     out["mx_a"], out["mx_b"], out["mx_sfa"], out["mx_sfb"] = qa, qb, ea, eb
     out["mx_c"] = (da.reshape(m, k) @ db.reshape(n, k).T).astype(np.float32)
 
+    # ---- a16w16 siblings: bf16 operands (ml_dtypes bfloat16), float64 GEMM, numpy-reshape shuffle ----
+    m, n, k = 24, 48, 128
+    a16 = rng.uniform(0.0, 1.0, (m, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    b16 = rng.uniform(-0.5, 0.5, (n, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    out["bf_a"], out["bf_b"] = a16.view(np.uint16), b16.view(np.uint16)
+    c64 = a16.astype(np.float64) @ b16.astype(np.float64).T
+    out["bf_c_f32"] = c64.astype(np.float32)
+    out["bf_c_bf16"] = c64.astype(np.float32).astype(ml_dtypes.bfloat16).view(np.uint16)
+    kk, nn = 40, 32                                                      # [K, N] -> [N/16][K/8][16][8]
+    w = rng.integers(0, 65536, (kk, nn)).astype(np.uint16)
+    out["bf_shuffle_in_kn"] = w
+    out["bf_shuffle_out"] = np.ascontiguousarray(w.reshape(kk // 8, 8, nn // 16, 16).transpose(2, 0, 3, 1)).reshape(-1)
+
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print("wrote golden.npz with", len(out), "arrays,", os.path.getsize(os.path.join(HERE, "golden.npz")), "bytes")
 

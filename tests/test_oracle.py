@@ -160,3 +160,29 @@ def test_valid_vector_semantics(O):
     assert not O.valid_vector(ref, res, 0.1)
     e, r = O.max_err(np.array([1.0, -4.0], np.float32), np.array([1.5, -4.0], np.float32))
     assert e == 0.5 and r == 4.0
+
+
+def test_bf16_siblings_golden(O, G):
+    """a16w16 references and the bf16 shuffle against ml_dtypes / numpy-reshape fixtures."""
+    c = O.gemm_ref_nt_bf16(G["bf_a"], G["bf_b"], out_bf16=False)
+    e, r = O.max_err(G["bf_c_f32"], c)
+    assert e <= 1e-5 * r                                        # float64 vs sequential fp32 sums
+    cb = O.gemm_ref_nt_bf16(G["bf_a"], G["bf_b"], out_bf16=True)
+    diff = np.abs(cb.astype(np.int32) - G["bf_c_bf16"].astype(np.int32))
+    assert diff.max() <= 1                                      # at most one bf16 ulp where the fp32 sums differ
+    assert (diff == 0).mean() > 0.97
+    ck = O.gemm_ref_kn_bf16(G["bf_a"], np.ascontiguousarray(G["bf_b"].T), out_bf16=False)
+    assert np.array_equal(ck, c)                                # same sums in the same order
+    assert np.array_equal(O.shuffle_b_bf16(G["bf_shuffle_in_kn"]), G["bf_shuffle_out"])
+    assert np.array_equal(O.unshuffle_b_bf16(G["bf_shuffle_out"], 32, 40), G["bf_shuffle_in_kn"])
+    with pytest.raises(ValueError):
+        O.shuffle_b_bf16(np.zeros((12, 16), np.uint16))         # K % 8 != 0
+
+
+def test_bf16_shuffle_is_the_byte_shuffle_of_the_nk_view(O):
+    """In bytes the bf16 flat image equals the 8-bit flat image of the [N][2K]-byte matrix."""
+    k, n = 64, 48
+    w = (np.arange(k * n, dtype=np.uint32) * 2654435761 >> 7).astype(np.uint16).reshape(k, n)
+    flat16 = O.shuffle_b_bf16(w)
+    nk_bytes = np.ascontiguousarray(w.T).view(np.uint8).reshape(n, 2 * k)
+    assert np.array_equal(flat16.view(np.uint8), O.shuffle_b_nk(nk_bytes))
