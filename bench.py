@@ -456,6 +456,28 @@ def main():
         hbm_probe["measured_peaks_hbm_gbs"] = measured_peaks()["hbm_gbs"]
         del pb, pc
 
+    # ---- a16w16 sibling: bf16 GEMM at 8192^3 against the measured cuBLAS bf16 rate ----
+    a16w16 = None
+    if world == 1 and not args.no_decode:
+        bm = bn = bk = 8192
+        xa = (torch.randn(bm, bk, device=dev) * 0.5).to(torch.bfloat16)
+        xw = (torch.randn(bn, bk, device=dev) * 0.5).to(torch.bfloat16)
+        xo = torch.empty(bm, bn, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            api.gemm_a16w16(xa, xw, out=xo)
+        torch.cuda.synchronize()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(10):
+            api.gemm_a16w16(xa, xw, out=xo)
+        b1.record()
+        torch.cuda.synchronize()
+        bms = b0.elapsed_time(b1) / 10
+        btf = 2.0 * bm * bn * bk / bms / 1e9
+        a16w16 = {"m": bm, "n": bn, "k": bk, "ms": bms, "tflops": btf,
+                  "frac_of_measured_bf16": btf / measured_peaks()["bf16_tflops"]}
+        del xa, xw, xo
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(args.workload)
@@ -472,7 +494,7 @@ def main():
                        "seed": SEED},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "kernel_ms": kern_ms, "device_status": status,
-            "decode": decode, "act_quant": act_quant, "hbm_probe": hbm_probe,
+            "decode": decode, "act_quant": act_quant, "hbm_probe": hbm_probe, "a16w16": a16w16,
         }
         print(json.dumps(line))
     if world > 1:

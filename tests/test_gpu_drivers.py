@@ -79,3 +79,12 @@ def test_flatmm_weight_file_round_trip(drivers, tmp_path):
     bad = subprocess.run([os.path.join(drivers, "flatmm_a8w8"), "-m", "16", "-n", "2048", "-k", "1024", "-b", "1", "--scale", "block",
                           "--load-weights", wfile], capture_output=True, text=True)
     assert bad.returncode == 1 and "not what this run asks for" in bad.stderr
+
+
+def test_gemm_a16w16_driver(drivers):
+    out = run(drivers, "gemm_a16w16")                                   # reference defaults: 256x512x128, batch 8, bf16 out
+    assert "Launching GEMM kernel: M=256, N=512, K=128" in out
+    assert out.count("VALID") >= 9 and "ALL BATCHES VALID" in out and "FAIL" not in out
+    assert re.search(r"Kernel Performance: avg_time=\d+\.\d+ ms, \d+\.\d+ TFlops", out)
+    out = run(drivers, "gemm_a16w16", "--flat", "-m", "300", "-n", "1024", "-k", "512", "-b", "2")
+    assert "BIT-EXACT" in out and "ALL BATCHES VALID" in out and "Launching FlatMM kernel" in out
