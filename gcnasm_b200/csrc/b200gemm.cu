@@ -200,6 +200,7 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
     if (a->scale_mode < 0 || a->scale_mode > 3 || a->b_layout < 0 || a->b_layout > 1 || a->out_dtype < 0 ||
         a->out_dtype > 1 || a->tile_hint < 0 || a->tile_hint > 8)
         return B200_ERR_BAD_ARG;
+    if (ab16 && (a->scale_mode == B200_SCALE_BLOCK || a->scale_mode == B200_SCALE_MX)) return B200_ERR_UNSUPPORTED;
     if (a->m > 0x7FFFFFFF || a->n > 0x7FFFFFFF || a->k > 0x7FFFFFFF || a->batch > 65535) return B200_ERR_TOO_LARGE;
     if (a->stride_a < a->k || a->stride_c < a->n) return B200_ERR_BAD_ARG;
     // TMA: 16-byte aligned bases and row pitches
@@ -225,7 +226,6 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
         if (a->batch > 1 && (a->stride_sfa_batch % 16 != 0 || a->stride_sfb_batch % 16 != 0)) return B200_ERR_UNSUPPORTED;
     }
 
-    if (ab16 && (a->scale_mode == B200_SCALE_BLOCK || a->scale_mode == B200_SCALE_MX)) return B200_ERR_UNSUPPORTED;
     Plan pl{B200_TILE_128x128, 0, 1};
     const int64_t kblocks = (a->k + 127) / 128;
     const bool decode_ok = !ab16 && a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);

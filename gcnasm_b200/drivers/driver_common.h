@@ -48,6 +48,7 @@ struct Options {
     uint64_t seed = 1234;
     std::string scale = "";                        // none | tensor | block | mx (driver default if empty)
     std::string out = "f32";                       // f32 | bf16   (the reference writes fp32)
+    bool act_bf16 = false;                         // blockscale: activations arrive in bf16, fused quantiser
     std::string save_weights = "", load_weights = "";  // flatmm: weight file written after / read instead of the shuffle
     std::string dist = "ref";                      // ref: A~U[0,1) B~U[-.5,.5) as the reference; u11: U[-1,1]; n01: N(0,1)
     int tile = 0;
@@ -93,6 +94,7 @@ inline Options parse(int argc, char** argv, int default_verify) {
         else if (take(argc, argv, i, nullptr, "--save-weights", v)) o.save_weights = v;
         else if (take(argc, argv, i, nullptr, "--load-weights", v)) o.load_weights = v;
         else if (std::strcmp(argv[i], "--json") == 0) o.json = true;
+        else if (std::strcmp(argv[i], "--act-bf16") == 0) o.act_bf16 = true;
     }
     return o;
 }

@@ -4,7 +4,9 @@
 // "-m 4096" and "-m=4096" forms, verification off unless -v 1, absolute threshold 1e-3, the same
 // printed lines); the launch at :257 is replaced by b200_gemm_a8w8().
 // Additions: --dist n01|u11 quantises seeded source data with group amax/448 on the device;
-// --scale mx runs the MXFP8 1x32 E8M0 variant; --out bf16; --seed; --json.
+// --scale mx runs the MXFP8 1x32 E8M0 variant; --out bf16; --seed; --json; --act-bf16 (with --dist) hands the
+// activations over in bf16 and quantises them with the fused one-pass kernel (b200_quantize_act_bf16_1x128 /
+// _mx32) instead of the fp32 quantiser + re-layout.
 #include "driver_common.h"
 
 using namespace drv;
@@ -96,6 +98,20 @@ int main(int argc, char** argv) {
             b200_fill_normal(xa.data(), xa.size(), o.seed, 0);
             b200_fill_normal(xb.data(), xb.size(), o.seed, 1);
         }
+        uint16_t* dxa16 = nullptr;
+        if (o.act_bf16) {
+            // the activations exist in bf16 only: round the source once, keep the rounded values as the fp32 truth
+            std::vector<uint16_t> xa16(xa.size());
+#pragma omp parallel for schedule(static)
+            for (long long i = 0; i < static_cast<long long>(xa.size()); ++i) {
+                uint32_t u;
+                std::memcpy(&u, &xa[i], 4);
+                xa16[i] = static_cast<uint16_t>((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+                xa[i] = bf16_bits_to_f32(xa16[i]);
+            }
+            dxa16 = dev_upload(xa16.data(), xa16.size());
+            std::printf("Activations in bf16: fused quantiser (one pass, scales written as the GEMM reads them)\n");
+        }
         float* dxa = dev_upload(xa.data(), xa.size());
         float* dxb = dev_upload(xb.data(), xb.size());
         DRV_CUDA(cudaMalloc(&da, ha.size()));
@@ -106,10 +122,11 @@ int main(int argc, char** argv) {
             DRV_CUDA(cudaMalloc(&deb, N * K / 32));
             DRV_CUDA(cudaMalloc(&dmxa, b200_mx_sf_bytes(o.m, o.k)));
             DRV_CUDA(cudaMalloc(&dmxb, b200_mx_sf_bytes(o.n, o.k)));
-            DRV_B200(b200_quantize_mx32(dxa, da, dea, o.m, o.k, nullptr));
+            DRV_B200(b200_quantize_mx32(dxa, da, dea, o.m, o.k, nullptr));        // logical scales for the host check
             DRV_B200(b200_quantize_mx32(dxb, db, deb, o.n, o.k, nullptr));
-            DRV_B200(b200_mx_sf_relayout(dea, dmxa, o.m, o.k, nullptr));
             DRV_B200(b200_mx_sf_relayout(deb, dmxb, o.n, o.k, nullptr));
+            if (dxa16) DRV_B200(b200_quantize_act_bf16_mx32(dxa16, o.k, da, o.k, dmxa, o.m, o.k, nullptr));
+            else DRV_B200(b200_mx_sf_relayout(dea, dmxa, o.m, o.k, nullptr));
             hea.resize(M * K / 32);
             heb.resize(N * K / 32);
             DRV_CUDA(cudaMemcpy(hea.data(), dea, hea.size(), cudaMemcpyDeviceToHost));
@@ -120,7 +137,11 @@ int main(int argc, char** argv) {
             DRV_CUDA(cudaMalloc(&dsfa, hsfa.size() * 4));
             DRV_CUDA(cudaMalloc(&dsfb, hsfb.size() * 4));
             for (size_t b = 0; b < B; ++b) {
-                DRV_B200(b200_quantize_1x128(dxa + b * M * K, da + b * M * K, dsfa + b * KG * M, o.m, o.k, nullptr));
+                if (dxa16)
+                    DRV_B200(b200_quantize_act_bf16_1x128(dxa16 + b * M * K, o.k, da + b * M * K, o.k, dsfa + b * KG * M, o.m, o.m,
+                                                          o.k, nullptr));
+                else
+                    DRV_B200(b200_quantize_1x128(dxa + b * M * K, da + b * M * K, dsfa + b * KG * M, o.m, o.k, nullptr));
                 DRV_B200(b200_quantize_128x128(dxb + b * N * K, db + b * N * K, dsfb + b * NG * KG, o.n, o.k, nullptr));
             }
             DRV_CUDA(cudaMemcpy(hsfa.data(), dsfa, hsfa.size() * 4, cudaMemcpyDeviceToHost));
@@ -130,6 +151,7 @@ int main(int argc, char** argv) {
         DRV_CUDA(cudaMemcpy(hb.data(), db, hb.size(), cudaMemcpyDeviceToHost));
         cudaFree(dxa);
         cudaFree(dxb);
+        if (dxa16) cudaFree(dxa16);
     }
     void* dc = nullptr;
     DRV_CUDA(cudaMalloc(&dc, B * M * N * (bf16 ? 2 : 4)));

@@ -149,3 +149,38 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libb200gemm.so")
     with pytest.raises(ImportError):
         _lib.lib()
+
+
+def test_sibling_entry_argument_checks(native):
+    """a16w16 check, bf16 shuffle, fused activation quantisers, bandwidth probe: validation only (no launch)."""
+    from gcnasm_b200 import _lib as L
+
+    tile = C.c_int32(0)
+    chk = lambda a: native.b200_gemm_a16w16_check(C.byref(a), C.byref(tile))
+    assert chk(_args()) == L.OK and tile.value in (L.TILE_128x128, L.TILE_128x256, L.TILE_PAIR_256x256)
+    assert chk(_args(m=16)) == L.OK and tile.value != L.TILE_DECODE               # no bf16 skinny-M kernel
+    assert chk(_args(m=8192, n=8192, k=8192, stride_a=8192, stride_b=8192, stride_c=8192)) == L.OK
+    assert tile.value == L.TILE_PAIR_256x256
+    assert chk(_args(k=1004, stride_a=1004, stride_b=1004)) == L.ERR_UNSUPPORTED   # K % 8 != 0 (bf16 rows of 16-byte units)
+    assert chk(_args(k=1032, stride_a=1032, stride_b=1032)) == L.OK
+    assert chk(_args(scale_mode=L.SCALE_BLOCK, ptr_sfa=0x4000, ptr_sfb=0x5000, stride_sfa=256, stride_sfb=8)) == L.ERR_UNSUPPORTED
+    assert chk(_args(scale_mode=L.SCALE_TENSOR)) == L.OK
+    assert chk(_args(b_layout=L.B_FLAT_16x16, k=1056, stride_a=1056)) == L.ERR_UNSUPPORTED     # flat bf16 needs K % 64 == 0
+    assert chk(_args(b_layout=L.B_FLAT_16x16)) == L.OK
+    assert chk(_args(tile_hint=L.TILE_PAIR_256x224)) == L.ERR_UNSUPPORTED
+    assert native.b200_gemm_a16w16_check(None, None) == L.ERR_BAD_ARG
+
+    assert native.b200_shuffle_b_bf16(0x1000, 0x2000, 24, 16, 1, None) == L.ERR_UNSUPPORTED
+    assert native.b200_shuffle_b_bf16(0x1000, 0x2000, 16, 12, 1, None) == L.ERR_UNSUPPORTED
+    assert native.b200_shuffle_b_bf16(None, 0x2000, 16, 16, 1, None) == L.ERR_BAD_ARG
+
+    q = native.b200_quantize_act_bf16_1x128
+    assert q(0x1000, 256, 0x2000, 256, 0x3000, 8, 8, 200, None) == L.ERR_UNSUPPORTED      # K % 128
+    assert q(0x1000, 100, 0x2000, 256, 0x3000, 8, 8, 256, None) == L.ERR_BAD_ARG           # ldx < K
+    assert q(0x1000, 256, 0x2000, 256, 0x3000, 4, 8, 256, None) == L.ERR_BAD_ARG           # stride_sfa < M
+    assert q(0x1008, 256, 0x2000, 256, 0x3000, 8, 8, 256, None) == L.ERR_UNSUPPORTED      # 16-byte loads
+    assert q(None, 256, 0x2000, 256, 0x3000, 8, 8, 256, None) == L.ERR_BAD_ARG
+    assert native.b200_quantize_act_bf16_mx32(0x1000, 256, 0x2000, 256, 0x3000, 8, 200, None) == L.ERR_UNSUPPORTED
+
+    assert native.b200_membw_read(0x1000, 20, 0x2000, None) == L.ERR_UNSUPPORTED          # bytes % 16
+    assert native.b200_membw_copy(0x1000, None, 32, None) == L.ERR_BAD_ARG

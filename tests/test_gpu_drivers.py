@@ -88,3 +88,14 @@ def test_gemm_a16w16_driver(drivers):
     assert re.search(r"Kernel Performance: avg_time=\d+\.\d+ ms, \d+\.\d+ TFlops", out)
     out = run(drivers, "gemm_a16w16", "--flat", "-m", "300", "-n", "1024", "-k", "512", "-b", "2")
     assert "BIT-EXACT" in out and "ALL BATCHES VALID" in out and "Launching FlatMM kernel" in out
+
+
+def test_blockscale_driver_bf16_activations(drivers):
+    """--act-bf16: activations handed over in bf16 and quantised by the fused kernel; the driver's host check (which
+    reads the device-made operand and scales back) must still pass, for fp32 block scales and for MX."""
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "512", "-n", "768", "-k", "1024", "-b", "2", "-v", "1", "--dist", "n01",
+              "--act-bf16", "--out", "bf16")
+    assert "fused quantiser" in out and "FAIL" not in out and out.count("VALID") >= 2
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "300", "-n", "512", "-k", "512", "-b", "1", "-v", "1", "--scale", "mx",
+              "--act-bf16")
+    assert "fused quantiser" in out and "FAIL" not in out and "VALID" in out
