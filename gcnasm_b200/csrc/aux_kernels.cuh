@@ -319,7 +319,6 @@ __global__ void __launch_bounds__(256) act_quant_bf16_1x128_kernel(const uint16_
 #pragma unroll 1
     for (int r0 = 0; r0 < nrows; r0 += 4) {
         uint4 raw[4];
-        float gmax[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             raw[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -328,36 +327,27 @@ __global__ void __launch_bounds__(256) act_quant_bf16_1x128_kernel(const uint16_
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            // |x| of a bf16 value: clear the sign bits of both halves of the word, widen, take the maximum
-            const uint32_t w[4] = {raw[i].x & 0x7FFF7FFFu, raw[i].y & 0x7FFF7FFFu, raw[i].z & 0x7FFF7FFFu, raw[i].w & 0x7FFF7FFFu};
+            if (r0 + i >= nrows) break;                                  // uniform across the warp
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+            float v[8];
             float m = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u)));
+            for (int j = 0; j < 4; ++j) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                m = fmaxf(m, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+            }
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-            gmax[i] = m;                                                 // uniform within each half-warp
-        }
-        // the two IEEE operations per group (amax/448 and its reciprocal) are long instruction sequences: lane j of
-        // each half-warp does them for row r0 + (j & 3), and the four results are handed round by shuffles
-        const float msel = (lane & 2) ? ((lane & 1) ? gmax[3] : gmax[2]) : ((lane & 1) ? gmax[1] : gmax[0]);
-        const float scsel = msel > 0.0f ? __fdiv_rn(msel, 448.0f) : 1.0f;
-        const float rcsel = __frcp_rn(scsel);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float sc = __shfl_sync(0xFFFFFFFFu, scsel, (lane & 16) | i);
-            const float rc = __shfl_sync(0xFFFFFFFFu, rcsel, (lane & 16) | i);
-            const float sa = __shfl_sync(0xFFFFFFFFu, scsel, i), sb = __shfl_sync(0xFFFFFFFFu, scsel, 16 | i);
-            if (r0 + i >= nrows) break;                                  // uniform across the warp
+            const float sc = m > 0.0f ? __fdiv_rn(m, 448.0f) : 1.0f;     // one per half-warp
+            const float rc = __frcp_rn(sc);
             const bool fast = sc >= 0x1p-100f && sc <= 0x1p100f;
-            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-            uint32_t o2[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                o2[h] = f32x4_to_e4m3x4(div_by_scale(__uint_as_float(w[2 * h] << 16), sc, rc, fast),
-                                        div_by_scale(__uint_as_float(w[2 * h] & 0xFFFF0000u), sc, rc, fast),
-                                        div_by_scale(__uint_as_float(w[2 * h + 1] << 16), sc, rc, fast),
-                                        div_by_scale(__uint_as_float(w[2 * h + 1] & 0xFFFF0000u), sc, rc, fast));
-            if (live) reinterpret_cast<uint2*>(q + (row0 + r0 + i) * ldq + gpair * 128)[lane] = make_uint2(o2[0], o2[1]);
+            auto dv = [&](float val) { return div_by_scale(val, sc, rc, fast); };
+            uint2 out;
+            out.x = f32x4_to_e4m3x4(dv(v[0]), dv(v[1]), dv(v[2]), dv(v[3]));
+            out.y = f32x4_to_e4m3x4(dv(v[4]), dv(v[5]), dv(v[6]), dv(v[7]));
+            if (live) reinterpret_cast<uint2*>(q + (row0 + r0 + i) * ldq + gpair * 128)[lane] = out;
+            const float sa = __shfl_sync(0xFFFFFFFFu, sc, 0), sb = __shfl_sync(0xFFFFFFFFu, sc, 16);
             if (lane == r0 + i) {
                 my_a = sa;
                 my_b = sb;
