@@ -220,16 +220,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
         bool ok = true;
 
         if constexpr (MODE == MODE_BLOCK) {
-            // stage this CTA's scales: sf_smem[i*MT + j] = sfa[kb0+i][j], then nkb weight-block scales
+            // stage this CTA's combined scales: sf_smem[i*MT + j] = sfa[kb0+i][j] * sfb[ni][kb0+i] (the product the
+            // promotion multiplies by, formed once here instead of once per thread and group)
             const float* sfa_g = p.sfa + b * p.sfa_batch;
             const float* sfb_g = p.sfb + b * p.sfb_batch + static_cast<long long>(ni) * p.sfb_stride;
             for (int idx = et; idx < nkb * MT; idx += 128) {
                 const int i = idx / MT, j = idx - i * MT;
-                sf_smem[idx] = (j < p.m) ? __ldg(sfa_g + static_cast<long long>(kb0 + i) * p.sfa_stride + j) : 0.0f;
+                sf_smem[idx] = (j < p.m) ? __ldg(sfa_g + static_cast<long long>(kb0 + i) * p.sfa_stride + j) * __ldg(sfb_g + kb0 + i) : 0.0f;
             }
-            for (int i = et; i < nkb; i += 128) sf_smem[nkb * MT + i] = __ldg(sfb_g + kb0 + i);
             asm volatile("bar.sync 1, 128;" ::: "memory");   // epilogue warps only
 
+            // packed accumulators (token pairs); the TMEM loads of group j+1 run behind the FMAs of group j
+            unsigned long long acc2[MT / 2];
+#pragma unroll
+            for (int j = 0; j < MT / 2; ++j) acc2[j] = 0ull;
+            float vbuf[2][MT];
             uint32_t phase = 0;
             for (int i0 = 0; i0 < nkb && ok; i0 += Cfg::GB, ++phase) {
                 const int gb = (nkb - i0 < Cfg::GB) ? nkb - i0 : Cfg::GB;
@@ -240,31 +245,34 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
                     break;
                 }
                 tc_fence_after();
-                for (int j = 0; j < gb; ++j) {
-                    const int i = i0 + j;
-                    float v[MT];
+                const uint32_t tset = tmem_base + tmem_lane + set * Cfg::GB * MT;
 #pragma unroll
-                    for (int c = 0; c < MT / 16; ++c)
-                        tmem_ld16(tmem_base + tmem_lane + (set * Cfg::GB + j) * MT + c * 16, &v[c * 16]);
-                    tmem_ld_wait();
-                    if (j == gb - 1) {
-                        // the whole batch is in registers: the set goes back to the MMA issuer
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_acce0 + set * 8);
-                    }
-                    const float sb = sf_smem[nkb * MT + i];
-                    const float4* sa4 = reinterpret_cast<const float4*>(sf_smem + i * MT);
+                for (int c = 0; c < MT / 16; ++c) tmem_ld16(tset + c * 16, &vbuf[0][c * 16]);
 #pragma unroll
-                    for (int jj = 0; jj < MT; jj += 4) {
-                        const float4 sa = sa4[jj / 4];
-                        acc[jj + 0] = fmaf(v[jj + 0], sa.x * sb, acc[jj + 0]);
-                        acc[jj + 1] = fmaf(v[jj + 1], sa.y * sb, acc[jj + 1]);
-                        acc[jj + 2] = fmaf(v[jj + 2], sa.z * sb, acc[jj + 2]);
-                        acc[jj + 3] = fmaf(v[jj + 3], sa.w * sb, acc[jj + 3]);
+                for (int j = 0; j < Cfg::GB; ++j) {
+                    if (j < gb) {
+                        tmem_ld_wait();                                  // group j is in vbuf[j & 1]
+                        if (j + 1 < gb) {
+#pragma unroll
+                            for (int c = 0; c < MT / 16; ++c) tmem_ld16(tset + (j + 1) * MT + c * 16, &vbuf[(j + 1) & 1][c * 16]);
+                        } else {
+                            // the whole batch has left TMEM: the set goes back to the MMA issuer
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_acce0 + set * 8);
+                        }
+                        const float4* s4 = reinterpret_cast<const float4*>(sf_smem + (i0 + j) * MT);
+#pragma unroll
+                        for (int jj = 0; jj < MT; jj += 4) {
+                            const float4 sc = s4[jj / 4];
+                            acc2[jj / 2] = ffma2(pack_f32x2(vbuf[j & 1][jj], vbuf[j & 1][jj + 1]), pack_f32x2(sc.x, sc.y), acc2[jj / 2]);
+                            acc2[jj / 2 + 1] = ffma2(pack_f32x2(vbuf[j & 1][jj + 2], vbuf[j & 1][jj + 3]), pack_f32x2(sc.z, sc.w), acc2[jj / 2 + 1]);
+                        }
                     }
                 }
             }
+#pragma unroll
+            for (int j = 0; j < MT / 2; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
         } else {
             if (nkb > 0) {
                 if (mbar_wait(bar_accf0, 0, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {

@@ -67,21 +67,6 @@ struct PairCfg {
     static_assert(ACC_COLS + SF_COLS <= 512, "TMEM overflow");
 };
 
-__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
-    unsigned long long d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-    return d;
-}
-__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-// d = a * b + c on two packed fp32 lanes
-__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-
 // Waits.  The single-thread roles poll (mbarrier.test_wait plus a short sleep), the epilogue warps use the
 // suspending try_wait.  Every wait uses the default CTA-scope acquire even when the arrivals come from the
 // partner CTA: a cluster-scope acquire was measured at ~430 clocks per wait, and each hand-off here is ordered
