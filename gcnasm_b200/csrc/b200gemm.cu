@@ -47,6 +47,11 @@ struct DeviceState {
     // cached buffers of b200_gemm_a8w8_host
     void* buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // b200_gemm_a8w8_host: second stream for the copy-back of finished row slabs, one event per slab
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t slab_done[16] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                 nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t copies_done = nullptr;
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -382,9 +387,9 @@ int max_pairs(Kernel kernel, int threads, int smem, int sm_count) {
     return n < sm_count / 2 ? n : sm_count / 2;
 }
 
-template <int BN, int MODE, int BL, int EW = 8>
+template <int BN, int MODE, int BL>
 int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
-    using Cfg = PairCfg<BN, MODE, BL, EW>;
+    using Cfg = PairCfg<BN, MODE, BL>;
     auto kernel = gemm_a8w8_pair_sm100_kernel<Cfg>;
     int rc = set_smem(kernel, Cfg::SMEM_BYTES);
     if (rc) return rc;
@@ -843,7 +848,6 @@ int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
     d.ptr_c = ds->buf[2];
     rc = validate(&d, ds->sm_count, &pl);
     if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(ds->buf[0], h->ptr_a, a_bytes, cudaMemcpyHostToDevice, st));
     CU_TRY(cudaMemcpyAsync(ds->buf[1], h->ptr_b, b_bytes, cudaMemcpyHostToDevice, st));
     if (sfa_bytes) {
         CU_TRY(cudaMemcpyAsync(ds->buf[3], h->ptr_sfa, sfa_bytes, cudaMemcpyHostToDevice, st));
@@ -862,9 +866,46 @@ int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
             d.ptr_scale_b = sc + 1;
         }
     }
-    rc = b200_gemm_a8w8(&d, st);
-    if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(h->ptr_c, ds->buf[2], c_bytes, cudaMemcpyDeviceToHost, st));
+    // Large single-batch problems run as row slabs: the copy-back of slab i (the largest transfer of the call)
+    // proceeds on a second stream while slab i+1 is uploaded and computed, so the two PCIe directions overlap.
+    // (MX scale atoms are indexed by the full M, so MX problems take the single-shot path.)
+    const int64_t slab_rows = ((h->m + 7) / 8 + 255) / 256 * 256;
+    const bool slabs = h->batch == 1 && h->m >= 2048 && h->scale_mode != B200_SCALE_MX && (h->m + slab_rows - 1) / slab_rows <= 16;
+    if (!slabs) {
+        CU_TRY(cudaMemcpyAsync(ds->buf[0], h->ptr_a, a_bytes, cudaMemcpyHostToDevice, st));
+        rc = b200_gemm_a8w8(&d, st);
+        if (rc) return rc;
+        CU_TRY(cudaMemcpyAsync(h->ptr_c, ds->buf[2], c_bytes, cudaMemcpyDeviceToHost, st));
+        CU_TRY(cudaStreamSynchronize(st));
+        return B200_OK;
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!ds->copy_stream) {
+            CU_TRY(cudaStreamCreateWithFlags(&ds->copy_stream, cudaStreamNonBlocking));
+            for (auto& e : ds->slab_done) CU_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            CU_TRY(cudaEventCreateWithFlags(&ds->copies_done, cudaEventDisableTiming));
+        }
+    }
+    int slab = 0;
+    for (int64_t r0 = 0; r0 < h->m; r0 += slab_rows, ++slab) {
+        const int64_t rows = (h->m - r0) < slab_rows ? (h->m - r0) : slab_rows;
+        b200_gemm_args s = d;
+        s.m = rows;
+        s.ptr_a = static_cast<const uint8_t*>(d.ptr_a) + r0 * h->stride_a;
+        s.ptr_c = static_cast<uint8_t*>(d.ptr_c) + static_cast<size_t>(r0) * h->stride_c * esz;
+        if (h->scale_mode == B200_SCALE_BLOCK) s.ptr_sfa = static_cast<const float*>(d.ptr_sfa) + r0;   // [K/128][M]: same pitch
+        CU_TRY(cudaMemcpyAsync(const_cast<void*>(s.ptr_a), static_cast<const uint8_t*>(h->ptr_a) + r0 * h->stride_a,
+                               static_cast<size_t>(rows * h->stride_a), cudaMemcpyHostToDevice, st));
+        rc = b200_gemm_a8w8(&s, st);
+        if (rc) return rc;
+        CU_TRY(cudaEventRecord(ds->slab_done[slab], st));
+        CU_TRY(cudaStreamWaitEvent(ds->copy_stream, ds->slab_done[slab], 0));
+        CU_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(h->ptr_c) + static_cast<size_t>(r0) * h->stride_c * esz, s.ptr_c,
+                               static_cast<size_t>(rows * h->stride_c) * esz, cudaMemcpyDeviceToHost, ds->copy_stream));
+    }
+    CU_TRY(cudaEventRecord(ds->copies_done, ds->copy_stream));
+    CU_TRY(cudaStreamWaitEvent(st, ds->copies_done, 0));
     CU_TRY(cudaStreamSynchronize(st));
     return B200_OK;
 }
@@ -1148,6 +1189,16 @@ int b200_release(void) {
     if (g_scratch[dev].ptr) cudaFree(g_scratch[dev].ptr);
     g_scratch[dev].ptr = nullptr;
     g_scratch[dev].cap = 0;
+    if (s.copy_stream) {
+        cudaStreamDestroy(s.copy_stream);
+        s.copy_stream = nullptr;
+        for (auto& e : s.slab_done) {
+            cudaEventDestroy(e);
+            e = nullptr;
+        }
+        cudaEventDestroy(s.copies_done);
+        s.copies_done = nullptr;
+    }
     return B200_OK;
 }
 const char* b200_version(void) { return "b200gemm 0.1 (sm_100a)"; }

@@ -18,14 +18,13 @@
 
 namespace b200 {
 
-// EW_ = epilogue warps per CTA: 8 (two per scheduler, 32 rows x BN/2 columns each) is what the launcher
-// instantiates.  16 (four per scheduler, 32 rows x BN/4 columns, 16-column TMEM loads, 112 registers) computes the
-// same results but measured 1475 against 2010 TFLOP/s on 8192^3 block-scale, so it is not built.
-template <int BN_, int MODE_, int BLAYOUT_, int EW_ = 8>
+// Eight epilogue warps per CTA: two per scheduler, 32 rows x BN/2 columns each.  (A 16-warp variant with 16-column
+// TMEM loads and 112 registers computed the same results at 1475 against 2010 TFLOP/s on 8192^3 block-scale.)
+template <int BN_, int MODE_, int BLAYOUT_>
 struct PairCfg {
     static constexpr bool AB16 = MODE_ == MODE_ACC16;               // bf16 operands: same bytes, kind::f16 MMAs
     static constexpr int BM = 128, BN = BN_, BK = 128, MODE = AB16 ? MODE_ACC : MODE_, BLAYOUT = BLAYOUT_;
-    static constexpr int EPI_WARPS = EW_, NSPLIT = EW_ / 4;         // column parts per row quadrant
+    static constexpr int EPI_WARPS = 8, NSPLIT = EPI_WARPS / 4;     // column parts per row quadrant
     static constexpr int BH = BN / 2;                               // B rows loaded by each CTA
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BH * BK;
@@ -41,7 +40,7 @@ struct PairCfg {
     static constexpr int TILE_STAGE_BYTES = TILE_TMA ? 128 * BN * 2 : 0;
     // per-warp staging of the plain-store epilogue; with a tile staging area it lives inside that area (a launch
     // uses one of the two store paths)
-    static constexpr int OUT_STAGE_BYTES = TILE_TMA ? 0 : EW_ * kOutStageBytesPerWarp;
+    static constexpr int OUT_STAGE_BYTES = TILE_TMA ? 0 : EPI_WARPS * kOutStageBytesPerWarp;
     static_assert(!TILE_TMA || 32 * NCH_ * 2 >= kOutStageBytesPerWarp, "per-warp tile area holds the plain-store staging");
     static constexpr int STAGES_RAW = (227 * 1024 - 2048 - OUT_STAGE_BYTES - TILE_STAGE_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -52,15 +51,13 @@ struct PairCfg {
     static constexpr int ACC_COLS = ACC_STAGES * BN;
     static constexpr int TMEM_COLS = (ACC_COLS + SF_COLS) <= 128 ? 128 : (ACC_COLS + SF_COLS) <= 256 ? 256 : 512;
     static constexpr int NCH = BN / NSPLIT;                         // columns owned by one epilogue thread
-    static constexpr int THREADS = 128 + 32 * EW_;
+    static constexpr int THREADS = 128 + 32 * EPI_WARPS;
     // setmaxnreg only redistributes the registers the CTA got at launch (THREADS x the per-thread count the
     // launch bound allows, a multiple of 8); an increase beyond that pool blocks forever
-    static constexpr int ROLE_REGS = (EW_ == 8) ? 40 : 32, EPI_REGS = (EW_ == 8) ? 232 : 112;
+    static constexpr int ROLE_REGS = 40, EPI_REGS = 232;
     static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;
-    static_assert(128 * ROLE_REGS + 32 * EW_ * EPI_REGS <= THREADS * LAUNCH_REGS, "setmaxnreg pool");
-    static constexpr int LW = (EW_ == 8) ? 32 : 16;                 // columns per TMEM load in block-scale mode
-    static_assert(EW_ == 8 || EW_ == 16, "8 or 16 epilogue warps");
-    static_assert(EW_ == 8 || (MODE == MODE_BLOCK && BN % 64 == 0), "16 epilogue warps: block-scale tiles only");
+    static_assert(128 * ROLE_REGS + 32 * EPI_WARPS * EPI_REGS <= THREADS * LAUNCH_REGS, "setmaxnreg pool");
+    static constexpr int LW = 32;                                   // columns per TMEM load in block-scale mode
     static_assert(BN % 32 == 0 && BN <= 256 && BN >= 64, "pair tile N: multiple of 32 in [64, 256]");
     static_assert(MODE != MODE_BLOCK || ACC_STAGES == 2, "block-scale needs two partial buffers");
     static_assert(MODE != MODE_MX || BN % 128 == 0, "MX scale atoms cover 128 columns");
@@ -84,7 +81,7 @@ static constexpr int kBlockIssuers = 2;
 __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
 #define B200_TRACE_EPI(slot)                                                                     \
     do {                                                                                         \
-        if (pair_id == 0 && lane == 0 && phase < 128 && ew < 8)                                  \
+        if (pair_id == 0 && lane == 0 && phase < 128)                                            \
             g_trace[((static_cast<int>(cta) * 8 + ew) * 128 + phase) * 8 + (slot)] = clock64();   \
     } while (0)
 #define B200_TRACE_MMA(slot)                                                                     \
@@ -349,7 +346,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     // when NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load
                     // has landed, before the last FMAs; the next group's scales are fetched after that arrive
                     // (an arrive waits for the thread's outstanding loads).
-                    constexpr int LW = Cfg::LW;                          // columns per load: 32, or 16 with 16 warps
+                    constexpr int LW = Cfg::LW;
                     constexpr int CFULL = NCH / LW, TAIL = NCH % LW;
                     constexpr int NLD = CFULL + (TAIL ? 1 : 0);          // loads per group
                     static_assert(TAIL == 0 || (LW == 32 && TAIL == 16), "tail load is 16 columns");

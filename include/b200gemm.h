@@ -92,7 +92,9 @@ int b200_gemm_a8w8_simple(const b200_gemm_args* args, void* cuda_stream);
 /* Whole reference main() data path with HOST buffers (hipMemcpy H2D -> launch -> hipMemcpy D2H,
  * gemm_a8w8_blockscale_host.cc:212-226,257,262): copies the operands in `args` (host pointers) to
  * device buffers owned by the library, runs the GEMM and copies C back; returns after the copy-back.
- * Device buffers are cached per device and grown on demand; b200_release() frees them.                  */
+ * Device buffers are cached per device and grown on demand; b200_release() frees them.  Single-batch problems
+ * with M >= 2048 (not MX) run as row slabs whose copy-back overlaps the next slab's upload and GEMM on a second,
+ * library-owned stream; the call still returns only when all of C is on the host.                        */
 int b200_gemm_a8w8_host(const b200_gemm_args* host_args, void* cuda_stream);
 
 /* No counterpart in the reference.  Skinny-M (M <= 64) GEMM with the same arguments and the same results as

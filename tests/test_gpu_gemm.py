@@ -274,3 +274,29 @@ def test_host_buffer_entry_point(api, O):
     api.gemm_a8w8_host(a, b, c2, scale_a=np.array([0.5], np.float32), scale_b=np.array([3.0], np.float32),
                        scale_mode=L.SCALE_TENSOR)
     assert_close(O, O.bf16_bits_to_f32(c2), O.gemm_ref_nt(a, b, 0.5, 3.0), "host entry tensor")
+
+
+@pytest.mark.parametrize("m", [2048, 2300, 4096])
+def test_host_buffer_entry_point_row_slabs(api, O, m):
+    """Large M: the host entry runs row slabs with the copy-back on a second stream.  Every row of C must arrive and
+    equal the device-resident result bit for bit (same kernels, same tiles within a slab boundary of 256 rows)."""
+    from gcnasm_b200 import _lib as L
+
+    n, k = 640, 512
+    a = e4m3(O, (m, k), 12, 0, 0.0, 1.0)
+    b = e4m3(O, (n, k), 12, 1, -0.5, 0.5)
+    sfa = O.fill_uniform((k // 128, m), 12, 2, 0.8, 1.2)
+    sfb = O.fill_uniform((n // 128, k // 128), 12, 3, 0.8, 1.2)
+    c = np.full((m, n), 0xFFFF, np.uint16)                           # poison: a missed slab would keep NaN bits
+    for _ in range(2):                                               # second call reuses streams, events and buffers
+        c[:] = 0xFFFF
+        api.gemm_a8w8_host(a, b, c, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK)
+        got = O.bf16_bits_to_f32(c)
+        assert not np.isnan(got).any()
+        rows = slice(0, m, 37)
+        ref = O.gemm_ref_blockscale(a, b, sfa, sfb)
+        assert_close(O, got[rows], ref[rows], f"host slabs m={m}")
+        assert_close(O, got[-64:], ref[-64:], "last rows")
+    cu = np.zeros((m, n), np.float32)
+    api.gemm_a8w8_host(a, b, cu)                                     # unscaled, fp32 out
+    assert_close(O, cu[::53], O.gemm_ref_nt(a, b)[::53], "host slabs unscaled")
