@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "sm100_ptx.cuh"
+
 namespace b200 {
 
 __device__ __forceinline__ uint8_t f32_to_e4m3(float x) {
@@ -243,6 +245,28 @@ __global__ void quant_1x128_kernel(const float* __restrict__ x, uint8_t* __restr
     reinterpret_cast<uint32_t*>(q + row * K + g * 128)[lane] =
         f32x4_to_e4m3x4(__fdiv_rn(v.x, s), __fdiv_rn(v.y, s), __fdiv_rn(v.z, s), __fdiv_rn(v.w, s));
     if (lane == 0) sfa[g * M + row] = s;
+}
+
+// ---- self-test of the bounded waits ---------------------------------------------------------------------------
+// Two threads wait on an mbarrier that nothing ever signals, with a short budget.  The first to run out sets the
+// CTA's abort flag and the status word; the other leaves through the abort flag or its own budget.  The kernel
+// then ends normally: this is how every pipeline wait in the GEMM kernels fails -- with a status, not a hang.
+__global__ void selftest_bounded_wait_kernel(int* status, unsigned long long budget_ns, int polling, int* returned) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0 || threadIdx.x == 32) {
+        ok = polling ? mbar_wait_poll<false, 64>(smem_u32(&bar), 0, &abort_flag, status, KSTAT_SELFTEST, budget_ns)
+                     : mbar_wait<false, 0>(smem_u32(&bar), 0, &abort_flag, status, KSTAT_SELFTEST, budget_ns);
+        atomicAdd(returned, ok ? 100 : 1);            // 2 when both waits gave up
+    }
+    __syncthreads();
 }
 
 // ---- HBM bandwidth probe ------------------------------------------------------------------------------------

@@ -1148,6 +1148,26 @@ int b200_last_status(void) {
     if (v != 0) CU_TRY(cudaMemset(ds->status_ptr, 0, sizeof(int)));
     return v;
 }
+int b200_selftest_bounded_wait(int64_t budget_us, int32_t polling, void* cuda_stream) {
+    if (budget_us < 100 || budget_us > 100000) return B200_ERR_BAD_ARG;          // 0.1 ms .. 100 ms
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if ((rc = ensure(ds, 6, 64))) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    int* returned = static_cast<int*>(ds->buf[6]);
+    CU_TRY(cudaMemsetAsync(returned, 0, sizeof(int), st));
+    selftest_bounded_wait_kernel<<<1, 64, 0, st>>>(ds->status_ptr, static_cast<unsigned long long>(budget_us) * 1000ull,
+                                                   polling, returned);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(st));
+    int n = 0;
+    CU_TRY(cudaMemcpy(&n, returned, sizeof(int), cudaMemcpyDeviceToHost));
+    return n == 2 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;       // both waits must have returned "gave up"
+}
 int b200_last_cuda_error(void) { return g_last_cuda; }
 int b200_weight_file_write(const char* path, int32_t b_layout, int32_t scale_mode, int64_t n, int64_t k, const void* data,
                            const void* scales) {

@@ -18,6 +18,7 @@ enum : int {
     KSTAT_TIMEOUT_ACC_E = 4,   // MMA issuer gave up waiting for a drained accumulator
     KSTAT_TIMEOUT_PEER  = 5,   // wait on the partner CTA of a pair expired
     KSTAT_TMEM_MISMATCH = 6,   // the two CTAs of a pair got different TMEM base addresses
+    KSTAT_SELFTEST      = 7,   // the self-test's wait on a barrier nobody signals ran out, as it must
 };
 
 // Wall-clock budget of one wait.  A wait that exceeds it records a status code, raises the
@@ -99,7 +100,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
 // scheduler.
 template <bool kClusterScope = false, int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, unsigned long long budget_ns = kWaitBudgetNs) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
@@ -110,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitBudgetNs) {
+            } else if (now - t0 > budget_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;
@@ -124,7 +125,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // thread on the same scheduler is itself waiting on a different barrier.
 template <bool kClusterScope = false, int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int* status, int code) {
+                                               int* status, int code, unsigned long long budget_ns = kWaitBudgetNs) {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (true) {
@@ -142,7 +143,7 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
             const unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitBudgetNs) {
+            } else if (now - t0 > budget_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;

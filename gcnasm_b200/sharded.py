@@ -52,6 +52,16 @@ class ColumnShardedGemm:
         self.quant_fn = quant_fn
         self._act_buf = None
 
+    def check_agreement(self, m: int, k: int) -> None:
+        """Host-side guard before a collective: every rank must be about to run the same (M, K).  A rank that
+        disagrees would otherwise leave the others inside a broadcast of the wrong size; here all ranks raise."""
+        if self.world == 1:
+            return
+        seen = [None] * self.world
+        dist.all_gather_object(seen, (int(m), int(k)), group=self.group)
+        if any(x != seen[0] for x in seen):
+            raise ValueError(f"ranks disagree on the activation shape: {seen}")
+
     def broadcast_activation(self, a: torch.Tensor, sfa: torch.Tensor, root: int = 0):
         """A [M,K] e4m3 bytes and SFA [K/128, M]: valid on ``root``, allocated (same shape) elsewhere."""
         if self.world > 1:
@@ -85,7 +95,7 @@ class ColumnShardedGemm:
         return buf, buf[:m * k].view(m, k), buf[m * k:].view(torch.float32).view(k // 128, m)
 
     def forward_bf16(self, x: Optional[torch.Tensor], m: int, k: int, device, root: int = 0,
-                     out: Optional[torch.Tensor] = None, gather: bool = False):
+                     out: Optional[torch.Tensor] = None, gather: bool = False, check: bool = False):
         """bf16 activations ``x`` [M,K] (needed on ``root`` only) -> this rank's ``C[:, shard]``.
 
         The root quantises straight into the broadcast buffer (fused quantiser: one read of x, one write of the
@@ -93,6 +103,8 @@ class ColumnShardedGemm:
         its GEMM on views of it: no fp32 copy of the activations, no separate scale tensor on the wire."""
         if m * k % 4 != 0:
             raise ValueError("M*K must be a multiple of 4 (the scales follow the bytes in one buffer)")
+        if check:
+            self.check_agreement(m, k)
         buf, a, sfa = self.activation_buffer(m, k, device)
         if self.rank == root:
             if x is None or tuple(x.shape) != (m, k):

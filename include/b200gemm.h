@@ -204,6 +204,11 @@ void b200_fill_normal(float* host_out, size_t count, uint64_t seed, uint32_t ten
 /* Device status word of the current device: 0, or the code of the first bounded wait that expired
  * since the last call (which also clears it).  Synchronises the device.                                  */
 int b200_last_status(void);
+/* Self-test of the failure path: a one-block kernel waits, with a budget of `budget_us` (100..100000), on a barrier
+ * that nothing signals (polling != 0: the test_wait flavour).  Returns B200_OK when both waiting threads gave up;
+ * afterwards b200_last_status() reports 7 (the self-test's code) once, and the context stays usable.  No part of
+ * the reference corresponds to this (its kernels have no waits that can be bounded).                          */
+int b200_selftest_bounded_wait(int64_t budget_us, int32_t polling, void* cuda_stream);
 int b200_last_cuda_error(void);
 const char* b200_strerror(int code);
 int b200_sm_count(void);

@@ -95,3 +95,68 @@ def test_column_sharded_gemm_world2(tmp_path, O):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert open(tmp_path / f"ok{r}").read() == "1"
+
+
+# ---- failures are made on the host: a rank that disagrees, a rank that leaves; nothing touches a GPU -----------
+def _worker_disagree(rank, world, port, tmp):
+    import sys
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from gcnasm_b200.sharded import ColumnShardedGemm
+
+    op = ColumnShardedGemm(torch.zeros(128, 256, dtype=torch.uint8), torch.zeros(1, 2), 256, gemm_fn=lambda *a: None,
+                           quant_fn=lambda *a: None, out_dtype=torch.float32)
+    k = 256 if rank == 0 else 384                     # rank 1 is about to run another problem
+    try:
+        op.forward_bf16(torch.zeros(16, k, dtype=torch.bfloat16), 16, k, "cpu", check=True)
+        verdict = "no error"
+    except ValueError as e:
+        verdict = "ValueError" if "disagree" in str(e) else f"other: {e}"
+    open(os.path.join(tmp, f"v{rank}"), "w").write(verdict)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_that_disagree_raise_on_every_rank(tmp_path):
+    world = 2
+    mp.spawn(_worker_disagree, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"v{r}").read() == "ValueError"
+
+
+def _worker_leaves(rank, world, port, tmp):
+    import datetime
+    import sys
+    import time
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from gcnasm_b200.sharded import ColumnShardedGemm
+
+    dist.barrier()
+    if rank == 1:
+        os._exit(0)                                   # leaves between steps, with no collective of its own in flight
+    op = ColumnShardedGemm(torch.zeros(128, 256, dtype=torch.uint8), torch.zeros(1, 2), 256, gemm_fn=lambda *a: None,
+                           out_dtype=torch.float32)
+    t0 = time.time()
+    try:
+        op(torch.zeros(16, 256, dtype=torch.uint8), torch.zeros(2, 16))
+        verdict = "no error"
+    except Exception as e:                            # gloo: connection closed by peer / timed out
+        verdict = f"error after {time.time() - t0:.1f}s"
+    open(os.path.join(tmp, "v0"), "w").write(verdict)
+    os._exit(0)                                       # the group is broken: no orderly shutdown
+
+
+def test_rank_that_leaves_ends_the_next_collective_with_an_error(tmp_path):
+    """The survivor's next broadcast fails within the process-group timeout instead of waiting forever."""
+    world = 2
+    mp.spawn(_worker_leaves, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    verdict = open(tmp_path / "v0").read()
+    assert verdict.startswith("error after"), verdict
+    assert float(verdict.split()[2][:-1]) < 30.0
