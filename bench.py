@@ -142,8 +142,9 @@ def cpu_reference_arm(args, workload, rank, world):
         "impl": "reference", "metric": "fp8_blockscale_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"{workload}_blockscale_M{m}_N{n}_K{k}", "note": "CPU restatement of the reference host loop; "
-                   "the HIP reference cannot be built in this image"},
+        "config": {"workload": f"{workload}_blockscale_M{m}_N{n}x{world}_K{k}", "scales": "A 1x128 fp32 [K/128][M], B 128x128 fp32",
+                   "out": "bf16", "seed": SEED, "note": "CPU restatement of the reference host loop (all host threads, row slab "
+                   "per step); the HIP reference cannot be built in this image"},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
