@@ -105,3 +105,42 @@ def test_scale_linearity_exact(api, O):
     bs = api.gemm_a8w8_blockscale(a, b, ones_a, ones_b, out_dtype=torch.float32)
     assert_close(O, bs.cpu().numpy(), base.cpu().numpy(), "unit block scales")
     status_ok(api)
+
+
+def test_config5_activation_quantise_full(api, O):
+    """Fused bf16 quantiser on config 5's activation matrix (16384 x 8192): sampled row blocks bit-exact against the
+    oracle, and the size-independent properties -- every scale is its group's amax/448, the largest magnitude of every
+    non-zero group encodes as +-448, the result does not change from run to run."""
+    m, k = 16384, 8192
+    x = torch.randn(m, k, device=DEV, dtype=torch.float32).mul_(2.0).to(torch.bfloat16)
+    x[100:228, 1024:1152] = 0                                       # whole zero groups
+    q, sfa = api.quantize_act_bf16_1x128(x)
+    q2, sfa2 = api.quantize_act_bf16_1x128(x)
+    assert torch.equal(q, q2) and torch.equal(sfa, sfa2)
+    for r0 in (0, 96, 8000, 16352):
+        bits = x[r0:r0 + 32].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        qr, sr = O.quant_1x128(O.bf16_bits_to_f32(bits))
+        assert np.array_equal(q[r0:r0 + 32].cpu().numpy(), qr), f"rows {r0}"
+        assert np.array_equal(sfa[:, r0:r0 + 32].cpu().numpy(), sr), f"scales of rows {r0}"
+    amax = x.float().abs().view(m, k // 128, 128).amax(dim=2)                       # [M, K/128]
+    want = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax)).t().contiguous()
+    assert torch.equal(sfa, want)
+    mag = (q.view(m, k // 128, 128) & 0x7F).amax(dim=2)                             # e4m3 magnitude bits
+    assert torch.equal(mag[amax > 0], torch.full_like(mag[amax > 0], 0x7E))          # 448 = 0x7E
+    assert int(mag[amax == 0].max()) == 0
+
+
+def test_a16w16_large_sampled_rows(api, O):
+    """bf16 sibling at 4096^3: sampled rows against the oracle, determinism, N-shard consistency."""
+    m = n = k = 4096
+    a = (torch.randn(m, k, device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, device=DEV) * 0.5).to(torch.bfloat16)
+    c = api.gemm_a16w16(a, b, out_dtype=torch.float32)
+    status_ok(api)
+    hb = b.view(torch.int16).cpu().numpy().view(np.uint16)
+    for r in _rows(m, 4, 5):
+        ha = a[r:r + 1].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        assert_close(O, c[r:r + 1].cpu().numpy(), O.gemm_ref_nt_bf16(ha, hb, out_bf16=False), f"row {r}")
+    assert torch.equal(c, api.gemm_a16w16(a, b, out_dtype=torch.float32))
+    shard = api.gemm_a16w16(a, b[1024:2048], out_dtype=torch.float32)
+    assert torch.equal(shard, c[:, 1024:2048])
