@@ -18,6 +18,7 @@ B_NK_ROWMAJOR, B_FLAT_16x16 = 0, 1
 OUT_F32, OUT_BF16 = 0, 1
 (TILE_AUTO, TILE_128x128, TILE_128x256, TILE_DECODE, TILE_PAIR_256x256, TILE_128x64, TILE_PAIR_256x128,
  TILE_PAIR_256x224, TILE_PAIR_256x192) = range(9)
+GEMM_INPUTS_READY = 1
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
 ERR_IO, ERR_CORRUPT = -7, -8
 
@@ -49,6 +50,7 @@ class GemmArgs(C.Structure):
         ("stride_sfa_batch", C.c_int64), ("stride_sfb_batch", C.c_int64),
         ("ptr_scale_a", C.c_void_p), ("ptr_scale_b", C.c_void_p),
         ("scale_mode", C.c_int32), ("b_layout", C.c_int32), ("out_dtype", C.c_int32), ("tile_hint", C.c_int32),
+        ("flags", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

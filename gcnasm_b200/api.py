@@ -40,7 +40,7 @@ def _out_code(dtype) -> int:
 
 
 def _gemm(a, b, *, n=None, sfa=None, sfb=None, scale_a=None, scale_b=None, scale_mode=L.SCALE_NONE,
-          b_layout=L.B_NK_ROWMAJOR, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False):
+          b_layout=L.B_NK_ROWMAJOR, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False, inputs_ready=False):
     a = _as_u8(a, "A")
     b = _as_u8(b, "B")
     squeeze = a.dim() == 2
@@ -108,26 +108,30 @@ def _gemm(a, b, *, n=None, sfa=None, sfb=None, scale_a=None, scale_b=None, scale
                 keep.append(s)
     args.scale_mode, args.b_layout = scale_mode, b_layout
     args.out_dtype, args.tile_hint = _out_code(out.dtype), tile
+    args.flags = L.GEMM_INPUTS_READY if inputs_ready else 0
     fn = lib().b200_gemm_a8w8_simple if simple else lib().b200_gemm_a8w8
     check(fn(C.byref(args), _stream()), "b200_gemm_a8w8_simple" if simple else "b200_gemm_a8w8")
     return out[0] if squeeze else out
 
 
 # ---- operators ---------------------------------------------------------------------------------
-def gemm_a8w8(a, b, scale_a=None, scale_b=None, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False):
-    """``C = (A . B^T) [* scale_a * scale_b]``.  Without scales this is the reference's gemm_a8w8_8wave."""
+def gemm_a8w8(a, b, scale_a=None, scale_b=None, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False,
+              inputs_ready=False):
+    """``C = (A . B^T) [* scale_a * scale_b]``.  Without scales this is the reference's gemm_a8w8_8wave.
+    ``inputs_ready``: see ``B200_GEMM_INPUTS_READY`` in the header (operands not written by work still in flight)."""
     mode = L.SCALE_TENSOR if (scale_a is not None or scale_b is not None) else L.SCALE_NONE
     return _gemm(a, b, scale_a=scale_a, scale_b=scale_b, scale_mode=mode, out=out, out_dtype=out_dtype, tile=tile,
-                 simple=simple)
+                 simple=simple, inputs_ready=inputs_ready)
 
 
 def gemm_a8w8_blockscale(a, b, sfa, sfb, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False,
-                         b_flat_n=None):
+                         b_flat_n=None, inputs_ready=False):
     """Block-scale GEMM: SFA fp32 ``[K/128, M]`` (1x128 groups, M contiguous), SFB fp32 ``[N/128, K/128]``."""
     if b_flat_n is not None:
         return _gemm(a, b, n=b_flat_n, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK, b_layout=L.B_FLAT_16x16, out=out,
-                     out_dtype=out_dtype, tile=tile, simple=simple)
-    return _gemm(a, b, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK, out=out, out_dtype=out_dtype, tile=tile, simple=simple)
+                     out_dtype=out_dtype, tile=tile, simple=simple, inputs_ready=inputs_ready)
+    return _gemm(a, b, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK, out=out, out_dtype=out_dtype, tile=tile, simple=simple,
+                 inputs_ready=inputs_ready)
 
 
 def gemm_a8w8_mx(a, b, sfa_atoms, sfb_atoms, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False):

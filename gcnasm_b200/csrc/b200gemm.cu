@@ -398,8 +398,21 @@ int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
     cudaGetDevice(&dev);
     if (pairs_cached[dev] == 0) pairs_cached[dev] = max_pairs(kernel, Cfg::THREADS, Cfg::SMEM_BYTES, sm_count);
     const int pairs = p.tiles_total < pairs_cached[dev] ? p.tiles_total : pairs_cached[dev];
-    kernel<<<2 * pairs, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
-    CU_TRY(cudaGetLastError());
+    // programmatic serialization: this launch may begin while its predecessor drains; the kernel decides what it
+    // does before the predecessor is complete (b200_gemm_flags)
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    std::memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CU_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
     g_launches.fetch_add(1);
     return B200_OK;
 }
@@ -641,6 +654,7 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
     p.tiles_total = static_cast<int>(total);
     p.kblocks = static_cast<int>((a->k + 127) / 128);
     p.out_dtype = a->out_dtype;
+    p.inputs_ready = (a->flags & B200_GEMM_INPUTS_READY) ? 1 : 0;
     p.status = ds->status_ptr;
     if (a->scale_mode == B200_SCALE_MX) {
         // atoms [K/128][rows/128][512 B]: strides in atoms, batch strides in bytes

@@ -123,6 +123,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
 
+    // Programmatic dependent launch: the next kernel on the stream may be scheduled as soon as every CTA of this
+    // one has passed this point and an SM is free.  What THIS kernel may do before its own predecessor has
+    // completed is decided by pdl_wait() below.
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full0 + s * 8, 1);          // leader's arrive.expect_tx; bytes from both CTAs
@@ -157,6 +161,9 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
 
     const int groups = (MODE == MODE_BLOCK) ? p.kblocks : 1;
     const int kb_per_group = (MODE == MODE_BLOCK) ? 1 : p.kblocks;
+    // Unless the caller vouched for the operands, nothing is read or written before the previous kernel is complete.
+    // With inputs_ready only the writes to C wait (in the epilogue, before the first tile is stored).
+    if (!p.inputs_ready) pdl_wait();
 
     if (!tmem_ok) {
         // fall through to the teardown
@@ -298,6 +305,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                     Cfg::OUT_STAGE_BYTES + ew * (32 * NCH * 2);
         uint8_t* tile_stage_gen = smem_gen + (tile_stage - smem_base);
         bool stores_pending = false;
+        bool c_ordered = !p.inputs_ready;           // writes to C must follow the previous kernel (see pdl_wait above)
         float tscale = 1.0f;
         if constexpr (MODE == MODE_ACC) {
             if (p.scale_a) tscale *= __ldg(p.scale_a);
@@ -404,6 +412,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     B200_TRACE_EPI(2);
                 }
+                if (!c_ordered) {
+                    pdl_wait();
+                    c_ordered = true;
+                }
                 if (ok && Cfg::TILE_TMA && p.c_tma) {
                     // bf16 tile -> shared memory in the 128-byte-swizzled layout of the TMA box (16-byte piece c of
                     // row r sits at piece c ^ (r & 7): conflict-free for the row-per-lane register layout), then
@@ -474,6 +486,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     break;
                 }
                 tc_fence_after();
+                if (!c_ordered) {
+                    pdl_wait();
+                    c_ordered = true;
+                }
                 const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
                 constexpr int CW = (NCH % 32 == 0) ? 32 : 16;      // columns per TMEM load
                 constexpr int NC = NCH / CW;

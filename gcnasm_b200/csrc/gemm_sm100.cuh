@@ -42,6 +42,7 @@ struct GemmParams {
     int tiles_m, tiles_n, tiles_total, kblocks;
     int out_dtype;
     int c_tma;                   // block-scale pair kernels: finished tiles leave through TMA bulk stores
+    int inputs_ready;            // pair kernels: operands do not depend on the previous kernel (see b200_gemm_flags)
     int* status;
 };
 

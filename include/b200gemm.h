@@ -72,7 +72,18 @@ typedef struct b200_gemm_args {
     int32_t b_layout;             /* b200_b_layout    */
     int32_t out_dtype;            /* b200_out_dtype   */
     int32_t tile_hint;            /* b200_tile_hint   */
+    int32_t flags;                /* b200_gemm_flags, 0 for the reference's behaviour */
+    int32_t reserved;             /* 0 */
 } b200_gemm_args;
+
+/* Launches on one stream are chained with programmatic dependent launch: a GEMM's prologue (barrier set-up, TMEM
+ * allocation) runs while the previous kernel drains, and by default everything else waits for the previous kernel
+ * to complete.  B200_GEMM_INPUTS_READY is the caller's promise that A, B and the scales of THIS call are not
+ * written by work still in flight on the stream (for instance consecutive GEMMs of independent requests, or
+ * weights and activations prepared earlier): the kernel then starts loading and multiplying at once -- on the SMs
+ * the previous launch no longer uses, e.g. during its last, partly filled wave of tiles -- and only its writes to C
+ * wait for the previous kernel.  Honoured by the 2-CTA tile kernels; other paths ignore it.                    */
+enum b200_gemm_flags { B200_GEMM_INPUTS_READY = 1 };
 
 /* Replaces the launches `gemm_a8w8_kernel<Traits><<<grid,block>>>(kargs)` (gemm_a8w8_8wave.cc:738),
  * `gemm_a8w8_blockscale_kernel<GemmTraits><<<grid,block>>>(kargs)` (gemm_a8w8_blockscale_host.cc:257)

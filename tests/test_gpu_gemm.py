@@ -300,3 +300,35 @@ def test_host_buffer_entry_point_row_slabs(api, O, m):
     cu = np.zeros((m, n), np.float32)
     api.gemm_a8w8_host(a, b, cu)                                     # unscaled, fp32 out
     assert_close(O, cu[::53], O.gemm_ref_nt(a, b)[::53], "host slabs unscaled")
+
+
+def test_chained_launches_with_inputs_ready(api, O):
+    """B200_GEMM_INPUTS_READY lets a launch start before its predecessor has finished.  Results must not change, and
+    two launches that write the same C must still land in order."""
+    m, n, k = 1024, 1792, 1024
+    sets = []
+    for j in range(3):
+        a, b = e4m3(O, (m, k), 20 + j, 0, 0.0, 1.0), e4m3(O, (n, k), 20 + j, 1, -0.5, 0.5)
+        sfa = O.fill_uniform((k // 128, m), 20 + j, 2, 0.8, 1.2)
+        sfb = O.fill_uniform((n // 128, k // 128), 20 + j, 3, 0.8, 1.2)
+        sets.append((T(a), T(b), T(sfa), T(sfb)))
+    want = [api.gemm_a8w8_blockscale(*s, out_dtype=torch.bfloat16) for s in sets]
+    torch.cuda.synchronize()
+    outs = [torch.empty_like(w) for w in want]
+    for rep in range(4):                                       # 12 launches back to back, no host synchronisation
+        for j, s in enumerate(sets):
+            api.gemm_a8w8_blockscale(*s, out=outs[j], inputs_ready=True)
+    status_ok(api)
+    for j in range(3):
+        assert torch.equal(outs[j], want[j]), f"set {j} changed under overlapped launches"
+    # same C written by consecutive launches of different problems: the last one wins
+    shared = torch.empty_like(want[0])
+    for rep in range(3):
+        for j, s in enumerate(sets):
+            api.gemm_a8w8_blockscale(*s, out=shared, inputs_ready=True)
+    status_ok(api)
+    assert torch.equal(shared, want[2])
+    # unscaled and MX kernels take the same launch path
+    c0 = api.gemm_a8w8(sets[0][0], sets[0][1], out_dtype=torch.float32)
+    c1 = api.gemm_a8w8(sets[0][0], sets[0][1], out_dtype=torch.float32, inputs_ready=True)
+    assert torch.equal(c0, c1)
