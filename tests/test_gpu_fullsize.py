@@ -123,8 +123,11 @@ def test_config5_activation_quantise_full(api, O):
         assert np.array_equal(q[r0:r0 + 32].cpu().numpy(), qr), f"rows {r0}"
         assert np.array_equal(sfa[:, r0:r0 + 32].cpu().numpy(), sr), f"scales of rows {r0}"
     amax = x.float().abs().view(m, k // 128, 128).amax(dim=2)                       # [M, K/128]
-    want = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax)).t().contiguous()
-    assert torch.equal(sfa, want)
+    # amax is exact; the division is done by numpy (IEEE fp32) -- torch's GPU division by a constant is not
+    # correctly rounded and differs in the last bit for some values
+    am = amax.cpu().numpy()
+    want = np.where(am > 0, am / np.float32(448.0), np.float32(1.0)).astype(np.float32).T
+    assert np.array_equal(sfa.cpu().numpy(), want)
     mag = (q.view(m, k // 128, 128) & 0x7F).amax(dim=2)                             # e4m3 magnitude bits
     assert torch.equal(mag[amax > 0], torch.full_like(mag[amax > 0], 0x7E))          # 448 = 0x7E
     assert int(mag[amax == 0].max()) == 0
