@@ -48,6 +48,7 @@ struct Options {
     uint64_t seed = 1234;
     std::string scale = "";                        // none | tensor | block | mx (driver default if empty)
     std::string out = "f32";                       // f32 | bf16   (the reference writes fp32)
+    bool overlap = false;                          // benchmark loop: launches flagged B200_GEMM_INPUTS_READY
     bool act_bf16 = false;                         // blockscale: activations arrive in bf16, fused quantiser
     std::string save_weights = "", load_weights = "";  // flatmm: weight file written after / read instead of the shuffle
     std::string dist = "ref";                      // ref: A~U[0,1) B~U[-.5,.5) as the reference; u11: U[-1,1]; n01: N(0,1)
@@ -95,6 +96,7 @@ inline Options parse(int argc, char** argv, int default_verify) {
         else if (take(argc, argv, i, nullptr, "--load-weights", v)) o.load_weights = v;
         else if (std::strcmp(argv[i], "--json") == 0) o.json = true;
         else if (std::strcmp(argv[i], "--act-bf16") == 0) o.act_bf16 = true;
+        else if (std::strcmp(argv[i], "--overlap") == 0) o.overlap = true;
     }
     return o;
 }
@@ -162,7 +164,11 @@ inline bool valid_relative(const float* ref, const float* res, long long count, 
 
 // benchmark_kernel (gemm_a8w8_8wave.cc:615-650): warm-up, then `iters` back-to-back launches between two
 // events on the default stream; TFlops = 2*M*N*K*batch / time.
-inline double benchmark(const b200_gemm_args& args, int warmup, int iters) {
+// `overlap`: the operands are the same static buffers in every iteration, so the launches may be flagged
+// B200_GEMM_INPUTS_READY (a launch starts while the previous one drains; writes to C stay ordered)
+inline double benchmark(const b200_gemm_args& args_in, int warmup, int iters, bool overlap = false) {
+    b200_gemm_args args = args_in;
+    if (overlap) args.flags |= B200_GEMM_INPUTS_READY;
     for (int i = 0; i < warmup; ++i) DRV_B200(b200_gemm_a8w8(&args, nullptr));
     cudaEvent_t e0, e1;
     DRV_CUDA(cudaEventCreate(&e0));

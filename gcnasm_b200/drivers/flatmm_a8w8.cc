@@ -171,7 +171,7 @@ int main(int argc, char** argv) {
         std::printf("\n[Overall] %s\n", all_valid ? "ALL BATCHES VALID" : "SOME BATCHES FAILED");
     }
     std::printf("\n");
-    const double ms = benchmark(args, o.warmup, o.iters);
+    const double ms = benchmark(args, o.warmup, o.iters, o.overlap);
     std::printf("\n");
     if (o.json) {
         const double bytes = (double)B * (N * K + M * K + (block ? 4.0 * (NG * KG + M * KG) : 0.0) + (bf16 ? 2.0 : 4.0) * M * N);

@@ -92,7 +92,7 @@ int main(int argc, char** argv) {
         std::printf("\n[Overall] %s\n", all_valid ? "ALL BATCHES VALID" : "SOME BATCHES FAILED");
     }
     std::printf("\n");
-    const double ms = benchmark(args, o.warmup, o.iters);
+    const double ms = benchmark(args, o.warmup, o.iters, o.overlap);
     std::printf("\n");
     if (o.json)
         std::printf("{\"driver\": \"gemm_a8w8_8wave\", \"m\": %d, \"n\": %d, \"k\": %d, \"batch\": %d, \"ms\": %.5f, \"tflops\": %.2f, \"valid\": %s}\n",

@@ -99,3 +99,10 @@ def test_blockscale_driver_bf16_activations(drivers):
     out = run(drivers, "gemm_a8w8_blockscale", "-m", "300", "-n", "512", "-k", "512", "-b", "1", "-v", "1", "--scale", "mx",
               "--act-bf16")
     assert "fused quantiser" in out and "FAIL" not in out and "VALID" in out
+
+
+def test_blockscale_driver_overlap_flag(drivers):
+    """--overlap flags the benchmark loop's launches as independent; the self-check and the result lines stay the same."""
+    out = run(drivers, "gemm_a8w8_blockscale", "-m", "1024", "-n", "1792", "-k", "1024", "-b", "1", "-v", "1", "--overlap")
+    assert "FAIL" not in out and "VALID" in out
+    assert re.search(r"Kernel Performance: avg_time=\d+\.\d+ ms, \d+\.\d+ TFlops", out)
