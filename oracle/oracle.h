@@ -15,7 +15,9 @@
  * formula only.  The quantisers, the per-tensor-scale epilogue, bf16 output and MXFP8
  * do not exist in the reference at all: for them PARITY IS UNPINNED by the reference
  * and is pinned instead by a second independent implementation (numpy + ml_dtypes and
- * NVIDIA's host cuda_fp8.h) in the test-suite.
+ * NVIDIA's host cuda_fp8.h) in the test-suite.  The a16w16 siblings (bf16 gemm_ref, bf16 shuffle_b) follow
+ * opus_gemm/gemm_a16w16_8wave.cc:584-595 and opus_fmm/flatmm_a16w16_gfx950.cc:571-582,623-666 line by line and are
+ * pinned the same way: by formula, and by ml_dtypes / numpy-reshape fixtures.
  */
 #ifndef B200GEMM_ORACLE_H
 #define B200GEMM_ORACLE_H
