@@ -292,7 +292,7 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
         int splits = 1;
         while (tiles * splits * 2 <= sm_count && splits * 2 <= kblocks && splits < 16) splits *= 2;
         if (a->scale_mode == B200_SCALE_BLOCK) {
-            const int64_t cap = (34 * 1024 / 4);
+            const int64_t cap = decode_sf_bytes(pl.mt) / 4;
             while (((kblocks + splits - 1) / splits) * (pl.mt + 1) > cap) {
                 splits *= 2;
                 if (splits > kblocks) return B200_ERR_TOO_LARGE;

@@ -39,6 +39,10 @@ struct DecodeParams {
     int* status;
 };
 
+// Shared-memory bytes for the staged scales of one CTA.  16-token blocks already reach the ten-stage cap of the ring
+// with 34 KB; wider token blocks get one more ring stage from a 24 KB area (config 4: 56 groups x 64 tokens = 14 KB).
+__host__ __device__ constexpr int decode_sf_bytes(int mt) { return mt <= 16 ? 34 * 1024 : 24 * 1024; }
+
 template <int MT_, int MODE_, int BLAYOUT_>
 struct DecodeCfg {
     static constexpr int MT = MT_, MODE = MODE_, BLAYOUT = BLAYOUT_;
@@ -46,7 +50,8 @@ struct DecodeCfg {
     static constexpr int W_BYTES = BNW * BK;
     static constexpr int X_BYTES = MT * BK;
     static constexpr int STAGE_BYTES = ((W_BYTES + X_BYTES + 1023) / 1024) * 1024;
-    static constexpr int SF_SMEM = 34 * 1024;               // token scales [K/128][MT] + weight scales [K/128]
+    // combined scales [K groups of this CTA][MT]; problems whose groups do not fit are split along K by the launcher
+    static constexpr int SF_SMEM = decode_sf_bytes(MT_);
     static constexpr int STAGES_RAW = (225 * 1024 - 1024 - SF_SMEM) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + SF_SMEM + 1024;
