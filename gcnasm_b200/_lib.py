@@ -18,7 +18,7 @@ B_NK_ROWMAJOR, B_FLAT_16x16 = 0, 1
 OUT_F32, OUT_BF16 = 0, 1
 (TILE_AUTO, TILE_128x128, TILE_128x256, TILE_DECODE, TILE_PAIR_256x256, TILE_128x64, TILE_PAIR_256x128,
  TILE_PAIR_256x224, TILE_PAIR_256x192) = range(9)
-GEMM_INPUTS_READY = 1
+GEMM_INPUTS_READY, GEMM_BATCH_READY = 1, 2
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
 ERR_IO, ERR_CORRUPT = -7, -8
 
@@ -32,7 +32,7 @@ EXPORTS = (
     "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32", "b200_membw_read", "b200_membw_copy",
     "b200_weight_file_write", "b200_weight_file_stat", "b200_weight_file_read",
     "b200_fill_uniform", "b200_fill_normal",
-    "b200_last_status", "b200_selftest_bounded_wait", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
+    "b200_flag_write", "b200_last_status", "b200_peek_status", "b200_selftest_bounded_wait", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
     "b200_version", "b200_launch_count",
 )
 
@@ -50,7 +50,8 @@ class GemmArgs(C.Structure):
         ("stride_sfa_batch", C.c_int64), ("stride_sfb_batch", C.c_int64),
         ("ptr_scale_a", C.c_void_p), ("ptr_scale_b", C.c_void_p),
         ("scale_mode", C.c_int32), ("b_layout", C.c_int32), ("out_dtype", C.c_int32), ("tile_hint", C.c_int32),
-        ("flags", C.c_int32), ("reserved", C.c_int32),
+        ("flags", C.c_int32), ("batch_epoch", C.c_int32),
+        ("ptr_batch_ready", C.c_void_p),
     ]
 
 
@@ -107,7 +108,9 @@ def lib() -> C.CDLL:
         "b200_mx_sf_bytes": (sz, [i64, i64]),
         "b200_fill_uniform": (None, [vp, sz, u64, u32, f32, f32]),
         "b200_fill_normal": (None, [vp, sz, u64, u32]),
+        "b200_flag_write": (i32, [vp, i32, vp]),
         "b200_last_status": (i32, []),
+        "b200_peek_status": (i32, []),
         "b200_selftest_bounded_wait": (i32, [i64, i32, vp]),
         "b200_last_cuda_error": (i32, []),
         "b200_strerror": (C.c_char_p, [i32]),

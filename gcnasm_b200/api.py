@@ -23,6 +23,27 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _same_device(*tensors) -> torch.device:
+    """Every CUDA operand of a call must live on ONE device, and that device must be the current one: the C side
+    picks its per-device state and the launch device with cudaGetDevice(), and the stream comes from
+    ``torch.cuda.current_stream()``.  A tensor of another GPU would put a foreign address into a tensor map and
+    fault on the device instead of raising here."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("operands must be CUDA tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"operands live on different devices: {dev} and {t.device}")
+    if dev is not None and dev.index != torch.cuda.current_device():
+        raise ValueError(f"operands live on {dev} but the current device is cuda:{torch.cuda.current_device()}; "
+                         "wrap the call in `with torch.cuda.device(tensor.device):`")
+    return dev
+
+
 def _as_u8(t: torch.Tensor, what: str) -> torch.Tensor:
     if t.dtype not in _FP8:
         raise TypeError(f"{what} must hold E4M3 bytes (uint8 or float8_e4m3fn), got {t.dtype}")
@@ -40,22 +61,26 @@ def _out_code(dtype) -> int:
 
 
 def _gemm(a, b, *, n=None, sfa=None, sfb=None, scale_a=None, scale_b=None, scale_mode=L.SCALE_NONE,
-          b_layout=L.B_NK_ROWMAJOR, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False, inputs_ready=False):
+          b_layout=L.B_NK_ROWMAJOR, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False, inputs_ready=False,
+          batch_ready=None, batch_epoch=0):
     a = _as_u8(a, "A")
     b = _as_u8(b, "B")
+    _same_device(a, b, sfa, sfb, scale_a, scale_b, out, batch_ready)
     squeeze = a.dim() == 2
     if squeeze:
         a = a.unsqueeze(0)
     batch, m, k = a.shape
     if a.stride(2) != 1:
         raise ValueError("A must be K-contiguous")
+    # a 2-D B (or scale tensor) given with a batched A is ONE operand shared by every batch (batch stride 0)
+    b_shared = batch > 1 and b_layout == L.B_NK_ROWMAJOR and b.dim() == 2
     if b_layout == L.B_NK_ROWMAJOR:
         if b.dim() == 2:
             b = b.unsqueeze(0)
-        if b.shape[0] != batch or b.shape[2] != k or b.stride(2) != 1:
-            raise ValueError("B must be [batch, N, K], K-contiguous, matching A")
+        if (not b_shared and b.shape[0] != batch) or b.shape[2] != k or b.stride(2) != 1:
+            raise ValueError("B must be [batch, N, K] (or [N, K], shared by all batches), K-contiguous, matching A")
         n = b.shape[1]
-        stride_b, stride_b_batch = b.stride(1), b.stride(0)
+        stride_b, stride_b_batch = b.stride(1), (0 if b_shared else b.stride(0))
     else:
         if n is None:
             raise ValueError("flat B needs n=")
@@ -82,13 +107,13 @@ def _gemm(a, b, *, n=None, sfa=None, sfb=None, scale_a=None, scale_b=None, scale
             sfb = sfb.unsqueeze(0)
         if sfa.dtype != torch.float32 or sfb.dtype != torch.float32:
             raise TypeError("block scales are float32")
-        if sfa.shape != (batch, k // 128, m) or sfb.shape != (batch, n // 128, k // 128):
-            raise ValueError("SFA must be [batch, K/128, M] and SFB [batch, N/128, K/128]")
+        if sfa.shape != (batch, k // 128, m) or sfb.shape != (1 if b_shared else batch, n // 128, k // 128):
+            raise ValueError("SFA must be [batch, K/128, M] and SFB [batch, N/128, K/128] ([N/128, K/128] with a shared B)")
         if sfa.stride(2) != 1 or sfb.stride(2) != 1:
             raise ValueError("scale tensors must be contiguous in their last dimension")
         args.ptr_sfa, args.ptr_sfb = sfa.data_ptr(), sfb.data_ptr()
         args.stride_sfa, args.stride_sfb = sfa.stride(1), sfb.stride(1)
-        args.stride_sfa_batch, args.stride_sfb_batch = sfa.stride(0), sfb.stride(0)
+        args.stride_sfa_batch, args.stride_sfb_batch = sfa.stride(0), (0 if b_shared else sfb.stride(0))
         keep += [sfa, sfb]
     elif scale_mode == L.SCALE_MX:
         need_a, need_b = lib().b200_mx_sf_bytes(m, k), lib().b200_mx_sf_bytes(n, k)
@@ -109,6 +134,12 @@ def _gemm(a, b, *, n=None, sfa=None, sfb=None, scale_a=None, scale_b=None, scale
     args.scale_mode, args.b_layout = scale_mode, b_layout
     args.out_dtype, args.tile_hint = _out_code(out.dtype), tile
     args.flags = L.GEMM_INPUTS_READY if inputs_ready else 0
+    if batch_ready is not None:
+        if batch_ready.dtype != torch.int32 or batch_ready.numel() < batch or not batch_ready.is_contiguous():
+            raise ValueError("batch_ready must be a contiguous int32 CUDA tensor with one word per batch")
+        args.flags |= L.GEMM_BATCH_READY
+        args.ptr_batch_ready, args.batch_epoch = batch_ready.data_ptr(), int(batch_epoch)
+        keep.append(batch_ready)
     fn = lib().b200_gemm_a8w8_simple if simple else lib().b200_gemm_a8w8
     check(fn(C.byref(args), _stream()), "b200_gemm_a8w8_simple" if simple else "b200_gemm_a8w8")
     return out[0] if squeeze else out
@@ -125,13 +156,28 @@ def gemm_a8w8(a, b, scale_a=None, scale_b=None, *, out=None, out_dtype=torch.bfl
 
 
 def gemm_a8w8_blockscale(a, b, sfa, sfb, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False,
-                         b_flat_n=None, inputs_ready=False):
-    """Block-scale GEMM: SFA fp32 ``[K/128, M]`` (1x128 groups, M contiguous), SFB fp32 ``[N/128, K/128]``."""
+                         b_flat_n=None, inputs_ready=False, batch_ready=None, batch_epoch=0):
+    """Block-scale GEMM: SFA fp32 ``[K/128, M]`` (1x128 groups, M contiguous), SFB fp32 ``[N/128, K/128]``.
+
+    With a batched A ``[batch, M, K]`` a 2-D ``b`` / ``sfb`` is shared by every batch.  ``batch_ready`` (int32, one
+    word per batch) makes the kernel wait for ``batch_ready[b] >= batch_epoch`` before it reads anything of batch b's
+    A or SFA (``B200_GEMM_BATCH_READY``: slabs that are still being delivered while the kernel runs)."""
     if b_flat_n is not None:
         return _gemm(a, b, n=b_flat_n, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK, b_layout=L.B_FLAT_16x16, out=out,
                      out_dtype=out_dtype, tile=tile, simple=simple, inputs_ready=inputs_ready)
     return _gemm(a, b, sfa=sfa, sfb=sfb, scale_mode=L.SCALE_BLOCK, out=out, out_dtype=out_dtype, tile=tile, simple=simple,
-                 inputs_ready=inputs_ready)
+                 inputs_ready=inputs_ready, batch_ready=batch_ready, batch_epoch=batch_epoch)
+
+
+def flag_write(flags: torch.Tensor, index: int, value: int) -> None:
+    """Stream-ordered write of ``value`` into ``flags[index]`` (int32) on the current stream: it happens when everything
+    queued on that stream before it has completed.  No kernel is launched (``b200_flag_write``)."""
+    if flags.dtype != torch.int32 or not flags.is_contiguous():
+        raise ValueError("flags must be a contiguous int32 CUDA tensor")
+    _same_device(flags)
+    if not (0 <= index < flags.numel()):
+        raise IndexError("flag index out of range")
+    check(lib().b200_flag_write(flags.data_ptr() + 4 * index, int(value), _stream()), "b200_flag_write")
 
 
 def gemm_a8w8_mx(a, b, sfa_atoms, sfb_atoms, *, out=None, out_dtype=torch.bfloat16, tile=L.TILE_AUTO, simple=False):
@@ -154,6 +200,7 @@ def shuffle_b(b: torch.Tensor, src: str = "kn") -> torch.Tensor:
     ``src='kn'``: ``b`` is ``[K, N]`` (what the reference's shuffle_b takes); ``src='nk'``: ``b`` is ``[N, K]``.
     """
     b = _as_u8(b, "B")
+    _same_device(b)
     if not b.is_contiguous() or b.dim() != 2:
         raise ValueError("B must be a contiguous 2-D tensor")
     k, n = (b.shape if src == "kn" else (b.shape[1], b.shape[0]))
@@ -164,6 +211,7 @@ def shuffle_b(b: torch.Tensor, src: str = "kn") -> torch.Tensor:
 
 def unshuffle_b(flat: torch.Tensor, n: int, k: int, dst: str = "kn") -> torch.Tensor:
     flat = _as_u8(flat, "flat B")
+    _same_device(flat)
     if not flat.is_contiguous() or flat.numel() != n * k:
         raise ValueError("flat B must be a contiguous image of N*K bytes")
     out = torch.empty((k, n) if dst == "kn" else (n, k), dtype=torch.uint8, device=flat.device)
@@ -176,6 +224,7 @@ def unshuffle_b(flat: torch.Tensor, n: int, k: int, dst: str = "kn") -> torch.Te
 def _f32(x: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
         raise TypeError("quantiser input must be a contiguous float32 CUDA tensor")
+    _same_device(x)
     return x
 
 
@@ -239,6 +288,7 @@ def quantize_act_bf16_1x128(x, q=None, sfa=None):
     pass.  `q` / `sfa` may be preallocated views (e.g. slices of a broadcast buffer); q rows may be strided."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise ValueError("x must be a 2-D bf16 tensor with unit column stride")
+    _same_device(x, q, sfa)
     m, k = x.shape
     if q is None:
         q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
@@ -257,6 +307,7 @@ def quantize_act_bf16_mx32(x):
     """Fused MX activation quantiser: bf16 [R,K] -> (q [R,K] uint8, scale atoms for the MX GEMM) in one pass."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise ValueError("x must be a 2-D bf16 tensor with unit column stride")
+    _same_device(x)
     r, k = x.shape
     q = torch.empty((r, k), dtype=torch.uint8, device=x.device)
     atoms = torch.empty(lib().b200_mx_sf_bytes(r, k), dtype=torch.uint8, device=x.device)
@@ -273,6 +324,7 @@ def gemm_a16w16(a, b, scale_a=None, scale_b=None, *, n=None, flat=False, out=Non
     image made by :func:`shuffle_b_bf16` (then ``n=`` is required)."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("A and B must be torch.bfloat16")
+    _same_device(a, b, scale_a, scale_b, out)
     squeeze = a.dim() == 2
     if squeeze:
         a = a.unsqueeze(0)
@@ -325,6 +377,7 @@ def shuffle_b_bf16(b: torch.Tensor, src: str = "kn") -> torch.Tensor:
     ``[N/16][K/8][16][8]`` (``opus_fmm/flatmm_a16w16_gfx950.cc:623-666``)."""
     if b.dtype != torch.bfloat16 or not b.is_contiguous() or b.dim() != 2:
         raise ValueError("B must be a contiguous 2-D bf16 tensor")
+    _same_device(b)
     k, n = (b.shape if src == "kn" else (b.shape[1], b.shape[0]))
     out = torch.empty(n * k, dtype=torch.bfloat16, device=b.device)
     check(lib().b200_shuffle_b_bf16(b.data_ptr(), out.data_ptr(), n, k, 1 if src == "kn" else 0, _stream()),
@@ -335,6 +388,7 @@ def shuffle_b_bf16(b: torch.Tensor, src: str = "kn") -> torch.Tensor:
 def unshuffle_b_bf16(flat: torch.Tensor, n: int, k: int, dst: str = "kn") -> torch.Tensor:
     if flat.dtype != torch.bfloat16 or not flat.is_contiguous() or flat.numel() != n * k:
         raise ValueError("flat B must be a contiguous bf16 image of N*K values")
+    _same_device(flat)
     out = torch.empty((k, n) if dst == "kn" else (n, k), dtype=torch.bfloat16, device=flat.device)
     check(lib().b200_unshuffle_b_bf16(flat.data_ptr(), out.data_ptr(), n, k, 1 if dst == "kn" else 0, _stream()),
           "b200_unshuffle_b_bf16")
@@ -345,6 +399,7 @@ def unshuffle_b_bf16(flat: torch.Tensor, n: int, k: int, dst: str = "kn") -> tor
 def membw_read(buf: torch.Tensor, word_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Streams `buf` once (read only); returns a 1-element int32 tensor holding the sum of its 32-bit words
     mod 2^32 (added to `word_sum` when given)."""
+    _same_device(buf, word_sum)
     if word_sum is None:
         word_sum = torch.zeros(1, dtype=torch.int32, device=buf.device)
     check(lib().b200_membw_read(buf.data_ptr(), buf.numel() * buf.element_size(), word_sum.data_ptr(), _stream()),
@@ -354,6 +409,7 @@ def membw_read(buf: torch.Tensor, word_sum: Optional[torch.Tensor] = None) -> to
 
 def membw_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     """Streams `src` into `dst` (read + write)."""
+    _same_device(src, dst)
     nbytes = src.numel() * src.element_size()
     if dst.numel() * dst.element_size() != nbytes:
         raise ValueError("src and dst differ in size")
@@ -408,6 +464,11 @@ def gemm_a8w8_host(a: np.ndarray, b: np.ndarray, c: np.ndarray, *, sfa=None, sfb
 
 def last_status() -> int:
     return lib().b200_last_status()
+
+
+def peek_status() -> int:
+    """The device status word without synchronising the device and without clearing it."""
+    return lib().b200_peek_status()
 
 
 def launch_count() -> int:

@@ -52,6 +52,8 @@ struct DeviceState {
     cudaEvent_t slab_done[16] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                                  nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaEvent_t copies_done = nullptr;
+    cudaStream_t peek_stream = nullptr;   // b200_peek_status: reads the status word without waiting for other streams
+    std::mutex host_entry_mu;             // b200_gemm_a8w8_host: one caller at a time per device (shared staging buffers)
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -60,6 +62,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+typedef CUresult (*StreamWriteValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+StreamWriteValue32Fn g_write_value32 = nullptr;     // null when the driver does not offer stream memory operations
+
+__global__ void flag_write_kernel(int* flag, int value) {
+    *flag = value;
+    __threadfence_system();
+}
 
 int device_state(DeviceState** out) {
     int dev = 0;
@@ -93,7 +102,14 @@ int device_state(DeviceState** out) {
             CU_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
             if (q != cudaDriverEntryPointSuccess || !fn) return B200_ERR_NO_DEVICE;
             g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            void* wv = nullptr;
+            if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &wv, cudaEnableDefault, &q) == cudaSuccess &&
+                q == cudaDriverEntryPointSuccess && wv)
+                g_write_value32 = reinterpret_cast<StreamWriteValue32Fn>(wv);
+            else
+                cudaGetLastError();
         }
+        CU_TRY(cudaStreamCreateWithFlags(&s.peek_stream, cudaStreamNonBlocking));
         s.init = true;
     }
     *out = &s;
@@ -231,9 +247,18 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
         if (a->batch > 1 && (a->stride_sfa_batch % 16 != 0 || a->stride_sfb_batch % 16 != 0)) return B200_ERR_UNSUPPORTED;
     }
 
+    // slabs that are still arriving, and one B for every batch: the 2-CTA tile kernels only
+    const bool batch_ready = (a->flags & B200_GEMM_BATCH_READY) != 0;
+    const bool b_shared = a->batch > 1 && a->stride_b_batch == 0;
+    const bool pair_only = batch_ready || b_shared;
+    if (batch_ready && !a->ptr_batch_ready) return B200_ERR_BAD_ARG;
+    if (batch_ready && (ab16 || a->scale_mode == B200_SCALE_MX)) return B200_ERR_UNSUPPORTED;
+    if (b_shared && a->scale_mode == B200_SCALE_BLOCK && a->stride_sfb_batch != 0) return B200_ERR_BAD_ARG;
+    if (pair_only && a->m <= 128) return B200_ERR_UNSUPPORTED;
+
     Plan pl{B200_TILE_128x128, 0, 1};
     const int64_t kblocks = (a->k + 127) / 128;
-    const bool decode_ok = !ab16 && a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
+    const bool decode_ok = !pair_only && !ab16 && a->m <= 64 && a->scale_mode != B200_SCALE_MX && (a->n % 16 == 0);
     int hint = a->tile_hint;
     if (hint == B200_TILE_DECODE && !decode_ok) return B200_ERR_UNSUPPORTED;
     if (hint == B200_TILE_128x64) return B200_ERR_UNSUPPORTED;
@@ -265,7 +290,7 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
             };
             if (mx) {
                 if (mx_pair_ok && a->m > 128) consider(B200_TILE_PAIR_256x256, 256, true);
-                consider(B200_TILE_128x128, 128, false);
+                if (!pair_only) consider(B200_TILE_128x128, 128, false);
             } else {
                 if (a->m > 128) {
                     consider(B200_TILE_PAIR_256x256, 256, true);
@@ -275,11 +300,16 @@ int validate(const b200_gemm_args* a, int sm_count, Plan* plan, bool ab16 = fals
                     consider(B200_TILE_PAIR_256x192, 192, true);
                     consider(B200_TILE_PAIR_256x128, 128, true);
                 }
-                consider(B200_TILE_128x256, 256, false);
-                consider(B200_TILE_128x128, 128, false);
+                if (!pair_only) {
+                    consider(B200_TILE_128x256, 256, false);
+                    consider(B200_TILE_128x128, 128, false);
+                }
             }
         }
     }
+    if (pair_only && !(hint == B200_TILE_PAIR_256x256 || hint == B200_TILE_PAIR_256x224 || hint == B200_TILE_PAIR_256x192 ||
+                       hint == B200_TILE_PAIR_256x128))
+        return B200_ERR_UNSUPPORTED;
     if (mx && !(hint == B200_TILE_128x128 || (hint == B200_TILE_PAIR_256x256 && mx_pair_ok))) return B200_ERR_UNSUPPORTED;
     // bf16 operands: pair 256x256 and the two single-CTA tiles are built
     if (ab16 && !(hint == B200_TILE_128x128 || hint == B200_TILE_128x256 || hint == B200_TILE_PAIR_256x256)) return B200_ERR_UNSUPPORTED;
@@ -442,76 +472,39 @@ int launch_decode_mt(int mt, const DecodeParams& p, int grid, cudaStream_t st) {
     }
 }
 
-// split-K scratch of the decode path, one per device, grown on demand
+// Split-K workspaces of the skinny-M path.  One per (device, stream): launches on different streams never share
+// partials.  A workspace that has been handed to a launch is never freed or moved before b200_release() -- a
+// launch still in flight, or a CUDA graph that captured one, keeps using the pointer it was given -- so a stream
+// that needs more gets an additional, larger one and the old one merely stops being handed out.
 struct Scratch {
-    float* ptr = nullptr;
-    size_t cap = 0;
+    int dev;
+    cudaStream_t stream;
+    float* ptr;
+    size_t cap;          // bytes
+    bool current;        // the one handed out for (dev, stream); older, smaller ones stay allocated until release
 };
-Scratch g_scratch[kMaxDevices];
+constexpr int kMaxScratch = 256;
+Scratch g_scratch[kMaxScratch];
+int g_scratch_count = 0;
 
-int run_decode(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
-    DecodeParams p;
-    std::memset(&p, 0, sizeof(p));
-    int rc;
-    if (a->b_layout == B200_B_NK_ROWMAJOR)
-        rc = make_rowmajor_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, 128);
-    else
-        rc = make_flat_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, 128);
-    if (rc) return rc;
-    rc = make_rowmajor_tmap(&p.tmap_x, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, pl.mt);
-    if (rc) return rc;
-    p.c = a->ptr_c;
-    p.sfa = static_cast<const float*>(a->ptr_sfa);
-    p.sfb = static_cast<const float*>(a->ptr_sfb);
-    p.scale_a = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_a : nullptr;
-    p.scale_b = a->scale_mode == B200_SCALE_TENSOR ? a->ptr_scale_b : nullptr;
-    p.ldc = a->stride_c;
-    p.c_batch = a->stride_c_batch;
-    p.sfa_stride = a->stride_sfa;
-    p.sfb_stride = a->stride_sfb;
-    p.sfa_batch = a->stride_sfa_batch;
-    p.sfb_batch = a->stride_sfb_batch;
-    p.m = static_cast<int>(a->m);
-    p.n = static_cast<int>(a->n);
-    p.k = static_cast<int>(a->k);
-    p.batch = static_cast<int>(a->batch);
-    p.tiles_n = static_cast<int>((a->n + 127) / 128);
-    p.kblocks = static_cast<int>((a->k + 127) / 128);
-    p.splits = pl.splits;
-    p.kb_per_split = (p.kblocks + pl.splits - 1) / pl.splits;
-    p.out_dtype = a->out_dtype;
-    p.status = ds->status_ptr;
-    if (pl.splits > 1) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const size_t need = static_cast<size_t>(pl.splits) * a->batch * a->m * a->n * sizeof(float);
-        std::lock_guard<std::mutex> lk(g_mu);
-        Scratch& s = g_scratch[dev];
-        if (s.cap < need) {
-            if (s.ptr) CU_TRY(cudaFree(s.ptr));
-            s.ptr = nullptr;
-            s.cap = 0;
-            CU_TRY(cudaMalloc(&s.ptr, need));
-            s.cap = need;
-        }
-        p.partial = s.ptr;
+int scratch_for(int dev, cudaStream_t st, size_t need, float** out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    Scratch* cur = nullptr;
+    for (int i = 0; i < g_scratch_count; ++i)
+        if (g_scratch[i].current && g_scratch[i].dev == dev && g_scratch[i].stream == st) cur = &g_scratch[i];
+    if (cur && cur->cap >= need) {
+        *out = cur->ptr;
+        return B200_OK;
     }
-    const int grid = p.tiles_n * p.batch * pl.splits;
-    const bool block = a->scale_mode == B200_SCALE_BLOCK;
-    if (a->b_layout == B200_B_NK_ROWMAJOR)
-        rc = block ? launch_decode_mt<MODE_BLOCK, BL_NK>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_NK>(pl.mt, p, grid, st);
-    else
-        rc = block ? launch_decode_mt<MODE_BLOCK, BL_FLAT>(pl.mt, p, grid, st) : launch_decode_mt<MODE_ACC, BL_FLAT>(pl.mt, p, grid, st);
-    if (rc) return rc;
-    if (pl.splits > 1) {
-        const long long per_split = static_cast<long long>(a->batch) * a->m * a->n;
-        const int threads = 256;
-        const unsigned blocks = static_cast<unsigned>((per_split + threads - 1) / threads);
-        decode_splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.partial, a->ptr_c, pl.splits, per_split, p.m, p.n,
-                                                               p.ldc, p.c_batch, p.out_dtype);
-        CU_TRY(cudaGetLastError());
-        g_launches.fetch_add(1);
-    }
+    if (g_scratch_count == kMaxScratch) return B200_ERR_TOO_LARGE;      // too many (stream, size) generations
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return B200_ERR_UNSUPPORTED;                                      // no allocation inside a capture
+    float* ptr = nullptr;
+    CU_TRY(cudaMalloc(&ptr, need));
+    if (cur) cur->current = false;
+    g_scratch[g_scratch_count++] = Scratch{dev, st, ptr, need, true};
+    *out = ptr;
     return B200_OK;
 }
 
@@ -524,11 +517,10 @@ constexpr size_t kStaticScratchFloats = 256 * 1024;                   // 1 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 
-int run_decode_static(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st) {
+int static_scratch(size_t need_floats, float** out) {
     int dev = 0;
     CU_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return B200_ERR_NO_DEVICE;
-    float* scratch = nullptr;
     {
         std::lock_guard<std::mutex> lk(g_mu);
         if (!g_static_scratch_ptr[dev]) {
@@ -536,13 +528,29 @@ int run_decode_static(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, 
             CU_TRY(cudaGetSymbolAddress(&sym, g_static_scratch));     // this device's copy of the array
             g_static_scratch_ptr[dev] = static_cast<float*>(sym);
         }
-        scratch = g_static_scratch_ptr[dev];
+        *out = g_static_scratch_ptr[dev];
     }
-    const size_t need = pl.splits > 1 ? static_cast<size_t>(pl.splits) * a->batch * a->m * a->n : 0;
-    if (need > kStaticScratchFloats) return B200_ERR_TOO_LARGE;
+    return need_floats > kStaticScratchFloats ? B200_ERR_TOO_LARGE : B200_OK;
+}
 
+// use_static: the split-K partials go to the fixed array above (b200_gemm_a8w8_decode_static) instead of a
+// cudaMalloc'd per-stream workspace.  Every element of the partials that the reduction reads is written by the
+// launch first, so neither kind of workspace is ever cleared.
+int run_decode(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStream_t st, bool use_static = false) {
     DecodeParams p;
     std::memset(&p, 0, sizeof(p));
+    const size_t need_floats = pl.splits > 1 ? static_cast<size_t>(pl.splits) * a->batch * a->m * a->n : 0;
+    if (use_static) {
+        float* scratch = nullptr;
+        int rc0 = static_scratch(need_floats, &scratch);
+        if (rc0) return rc0;
+        p.partial = pl.splits > 1 ? scratch : nullptr;
+    } else if (pl.splits > 1) {
+        int dev = 0;
+        CU_TRY(cudaGetDevice(&dev));
+        int rc0 = scratch_for(dev, st, need_floats * sizeof(float), &p.partial);
+        if (rc0) return rc0;
+    }
     int rc;
     if (a->b_layout == B200_B_NK_ROWMAJOR)
         rc = make_rowmajor_tmap(&p.tmap_w, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, 128);
@@ -571,10 +579,8 @@ int run_decode_static(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, 
     p.splits = pl.splits;
     p.kb_per_split = (p.kblocks + pl.splits - 1) / pl.splits;
     p.out_dtype = a->out_dtype;
+    p.inputs_ready = (a->flags & B200_GEMM_INPUTS_READY) ? 1 : 0;
     p.status = ds->status_ptr;
-    // every element of the partials that the reduction reads is written by this launch first, so nothing in
-    // the shared array has to be cleared between calls
-    p.partial = pl.splits > 1 ? scratch : nullptr;
     const int grid = p.tiles_n * p.batch * pl.splits;
     const bool block = a->scale_mode == B200_SCALE_BLOCK;
     if (a->b_layout == B200_B_NK_ROWMAJOR)
@@ -611,10 +617,12 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
     std::memset(&p, 0, sizeof(p));
     int rc = make_rowmajor_tmap(&p.tmap_a, a->ptr_a, a->m, a->k, a->stride_a, a->batch, a->stride_a_batch, 128);
     if (rc) return rc;
+    const bool b_shared = a->batch > 1 && a->stride_b_batch == 0;      // one B for every batch (validate(): pair tiles)
+    const int64_t b_batches = b_shared ? 1 : a->batch;
     if (a->b_layout == B200_B_NK_ROWMAJOR)
-        rc = make_rowmajor_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->stride_b, a->batch, a->stride_b_batch, BROWS);
+        rc = make_rowmajor_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->stride_b, b_batches, a->stride_b_batch, BROWS);
     else
-        rc = make_flat_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, a->batch, a->stride_b_batch, BROWS);
+        rc = make_flat_tmap(&p.tmap_b, a->ptr_b, a->n, a->k, b_batches, a->stride_b_batch, BROWS);
     if (rc) return rc;
     if (pair && a->scale_mode == B200_SCALE_MX) {
         // scale atoms as rows of 256 bytes; one atom = 2 rows
@@ -654,7 +662,12 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
     p.tiles_total = static_cast<int>(total);
     p.kblocks = static_cast<int>((a->k + 127) / 128);
     p.out_dtype = a->out_dtype;
-    p.inputs_ready = (a->flags & B200_GEMM_INPUTS_READY) ? 1 : 0;
+    p.inputs_ready = (a->flags & (B200_GEMM_INPUTS_READY | B200_GEMM_BATCH_READY)) ? 1 : 0;
+    p.b_shared = b_shared ? 1 : 0;
+    if (a->flags & B200_GEMM_BATCH_READY) {
+        p.batch_ready = reinterpret_cast<const int*>(a->ptr_batch_ready);
+        p.batch_epoch = a->batch_epoch;
+    }
     p.status = ds->status_ptr;
     if (a->scale_mode == B200_SCALE_MX) {
         // atoms [K/128][rows/128][512 B]: strides in atoms, batch strides in bytes
@@ -794,7 +807,7 @@ int b200_gemm_a8w8_decode_static(const b200_gemm_args* args, void* cuda_stream) 
     rc = validate(args, ds->sm_count, &pl);
     if (rc) return rc;
     if (pl.tile != B200_TILE_DECODE) return B200_ERR_UNSUPPORTED;      // only the skinny-M kernel has this variant
-    return run_decode_static(args, pl, ds, static_cast<cudaStream_t>(cuda_stream));
+    return run_decode(args, pl, ds, static_cast<cudaStream_t>(cuda_stream), true);
 }
 
 int b200_gemm_a8w8_simple(const b200_gemm_args* a, void* cuda_stream) {
@@ -829,27 +842,62 @@ int b200_gemm_a8w8_simple(const b200_gemm_args* a, void* cuda_stream) {
     return B200_OK;
 }
 
+// End of the synchronous host-buffer entry: wait for the stream, then look at the status word, so that a launch
+// that gave up (an expired wait, a pair whose CTAs disagreed on their tensor-memory address) is an error HERE and
+// not a silently wrong C.  The word is left for b200_last_status() to report and clear.
+static int host_entry_finish(DeviceState* ds, cudaStream_t st) {
+    CU_TRY(cudaStreamSynchronize(st));
+    int v = 0;
+    CU_TRY(cudaMemcpy(&v, ds->status_ptr, sizeof(int), cudaMemcpyDeviceToHost));
+    return v == 0 ? B200_OK : B200_ERR_DEVICE_TIMEOUT;
+}
+
+// a * b for non-negative operands, or -1 when the product does not fit in 2^46 bytes (64 TiB: far above any device)
+static int64_t mul_checked(int64_t a, int64_t b) {
+    if (a < 0 || b < 0) return -1;
+    if (a == 0 || b == 0) return 0;
+    if (a > (int64_t(1) << 46) / b) return -1;
+    return a * b;
+}
+
 int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
     Plan pl;
-    if (!h) return B200_ERR_BAD_ARG;
+    if (!h || !h->ptr_a || !h->ptr_b || !h->ptr_c) return B200_ERR_BAD_ARG;
+    if (h->flags & B200_GEMM_BATCH_READY) return B200_ERR_UNSUPPORTED;       // ready words are device memory
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-    const size_t esz = h->out_dtype == B200_OUT_BF16 ? 2 : 4;
-    const size_t a_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_a_batch * h->batch : h->stride_a * h->m);
-    const size_t b_bytes = static_cast<size_t>(h->b_layout == B200_B_FLAT_16x16
-                                                   ? (h->batch > 1 ? h->stride_b_batch * h->batch : h->n * h->k)
-                                                   : (h->batch > 1 ? h->stride_b_batch * h->batch : h->stride_b * h->n));
-    const size_t c_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_c_batch * h->batch : h->stride_c * h->m) * esz;
-    size_t sfa_bytes = 0, sfb_bytes = 0;
-    if (h->scale_mode == B200_SCALE_BLOCK) {
-        sfa_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_sfa_batch * h->batch : h->stride_sfa * (h->k / 128)) * 4;
-        sfb_bytes = static_cast<size_t>(h->batch > 1 ? h->stride_sfb_batch * h->batch : h->stride_sfb * (h->n / 128)) * 4;
-    } else if (h->scale_mode == B200_SCALE_MX) {
-        sfa_bytes = h->batch > 1 ? static_cast<size_t>(h->stride_sfa_batch * h->batch) : b200_mx_sf_bytes(h->m, h->k);
-        sfb_bytes = h->batch > 1 ? static_cast<size_t>(h->stride_sfb_batch * h->batch) : b200_mx_sf_bytes(h->n, h->k);
+    // validate before anything is allocated, copied or queued: the same checks as the device entry, run on a copy
+    // whose operand pointers are stand-ins with the alignment the library's own buffers will have
+    {
+        b200_gemm_args probe = *h;
+        probe.ptr_a = probe.ptr_b = probe.ptr_c = reinterpret_cast<void*>(uintptr_t(256));
+        if (h->scale_mode == B200_SCALE_BLOCK || h->scale_mode == B200_SCALE_MX) {
+            if (!h->ptr_sfa || !h->ptr_sfb) return B200_ERR_BAD_ARG;
+            probe.ptr_sfa = probe.ptr_sfb = reinterpret_cast<void*>(uintptr_t(256));
+        }
+        if ((rc = validate(&probe, ds->sm_count, &pl))) return rc;
+        if (h->b_layout == B200_B_NK_ROWMAJOR && h->stride_b < h->k) return B200_ERR_BAD_ARG;
     }
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const int64_t esz = h->out_dtype == B200_OUT_BF16 ? 2 : 4;
+    const int64_t a_sz = h->batch > 1 ? mul_checked(h->stride_a_batch, h->batch) : mul_checked(h->stride_a, h->m);
+    const int64_t b_sz = h->batch > 1 ? mul_checked(h->stride_b_batch, h->batch)
+                                      : (h->b_layout == B200_B_FLAT_16x16 ? mul_checked(h->n, h->k) : mul_checked(h->stride_b, h->n));
+    const int64_t c_sz = mul_checked(h->batch > 1 ? mul_checked(h->stride_c_batch, h->batch) : mul_checked(h->stride_c, h->m), esz);
+    int64_t sfa_sz = 0, sfb_sz = 0;
+    if (h->scale_mode == B200_SCALE_BLOCK) {
+        sfa_sz = mul_checked(h->batch > 1 ? mul_checked(h->stride_sfa_batch, h->batch) : mul_checked(h->stride_sfa, h->k / 128), 4);
+        sfb_sz = mul_checked(h->batch > 1 ? mul_checked(h->stride_sfb_batch, h->batch) : mul_checked(h->stride_sfb, h->n / 128), 4);
+    } else if (h->scale_mode == B200_SCALE_MX) {
+        sfa_sz = h->batch > 1 ? mul_checked(h->stride_sfa_batch, h->batch) : static_cast<int64_t>(b200_mx_sf_bytes(h->m, h->k));
+        sfb_sz = h->batch > 1 ? mul_checked(h->stride_sfb_batch, h->batch) : static_cast<int64_t>(b200_mx_sf_bytes(h->n, h->k));
+    }
+    if (a_sz <= 0 || b_sz <= 0 || c_sz <= 0 || sfa_sz < 0 || sfb_sz < 0) return B200_ERR_BAD_ARG;   // zero, negative or overflowing
+    const size_t a_bytes = static_cast<size_t>(a_sz), b_bytes = static_cast<size_t>(b_sz), c_bytes = static_cast<size_t>(c_sz);
+    const size_t sfa_bytes = static_cast<size_t>(sfa_sz), sfb_bytes = static_cast<size_t>(sfb_sz);
+    // the staging buffers, the copy stream and its events are per device: one caller at a time
+    std::lock_guard<std::mutex> entry(ds->host_entry_mu);
     {
         std::lock_guard<std::mutex> lk(g_mu);
         if ((rc = ensure(ds, 0, a_bytes)) || (rc = ensure(ds, 1, b_bytes)) || (rc = ensure(ds, 2, c_bytes)) ||
@@ -890,8 +938,7 @@ int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
         rc = b200_gemm_a8w8(&d, st);
         if (rc) return rc;
         CU_TRY(cudaMemcpyAsync(h->ptr_c, ds->buf[2], c_bytes, cudaMemcpyDeviceToHost, st));
-        CU_TRY(cudaStreamSynchronize(st));
-        return B200_OK;
+        return host_entry_finish(ds, st);
     }
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -920,8 +967,7 @@ int b200_gemm_a8w8_host(const b200_gemm_args* h, void* cuda_stream) {
     }
     CU_TRY(cudaEventRecord(ds->copies_done, ds->copy_stream));
     CU_TRY(cudaStreamWaitEvent(st, ds->copies_done, 0));
-    CU_TRY(cudaStreamSynchronize(st));
-    return B200_OK;
+    return host_entry_finish(ds, st);
 }
 
 // ---- layout ----------------------------------------------------------------------------------------
@@ -1162,6 +1208,33 @@ int b200_last_status(void) {
     if (v != 0) CU_TRY(cudaMemset(ds->status_ptr, 0, sizeof(int)));
     return v;
 }
+int b200_peek_status(void) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    int v = 0;
+    CU_TRY(cudaMemcpyAsync(&v, ds->status_ptr, sizeof(int), cudaMemcpyDeviceToHost, ds->peek_stream));
+    CU_TRY(cudaStreamSynchronize(ds->peek_stream));
+    return v;
+}
+int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream) {
+    if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) return B200_ERR_BAD_ARG;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (g_write_value32) {
+        const CUresult r = g_write_value32(reinterpret_cast<CUstream>(st), reinterpret_cast<CUdeviceptr>(flag),
+                                           static_cast<cuuint32_t>(value), 0 /* CU_STREAM_WRITE_VALUE_DEFAULT */);
+        if (r == CUDA_SUCCESS) return B200_OK;
+        g_last_cuda = 100000 + static_cast<int>(r);
+        return B200_ERR_CUDA;
+    }
+    flag_write_kernel<<<1, 1, 0, st>>>(flag, value);         // drivers without stream memory operations
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200_OK;
+}
 int b200_selftest_bounded_wait(int64_t budget_us, int32_t polling, void* cuda_stream) {
     if (budget_us < 100 || budget_us > 100000) return B200_ERR_BAD_ARG;          // 0.1 ms .. 100 ms
     DeviceState* ds = nullptr;
@@ -1220,9 +1293,14 @@ int b200_release(void) {
         s.buf[i] = nullptr;
         s.cap[i] = 0;
     }
-    if (g_scratch[dev].ptr) cudaFree(g_scratch[dev].ptr);
-    g_scratch[dev].ptr = nullptr;
-    g_scratch[dev].cap = 0;
+    {
+        int kept = 0;
+        for (int i = 0; i < g_scratch_count; ++i) {
+            if (g_scratch[i].dev == dev) cudaFree(g_scratch[i].ptr);
+            else g_scratch[kept++] = g_scratch[i];
+        }
+        g_scratch_count = kept;
+    }
     if (s.copy_stream) {
         cudaStreamDestroy(s.copy_stream);
         s.copy_stream = nullptr;

@@ -36,6 +36,7 @@ struct DecodeParams {
     int m, n, k, batch;
     int tiles_n, kblocks, splits, kb_per_split;
     int out_dtype;
+    int inputs_ready;            // the weights are not written by work still in flight on the stream (b200_gemm_flags)
     int* status;
 };
 
@@ -98,11 +99,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
     const int nkb = kb1 - kb0;
 
     // Consecutive decode GEMMs of a serving step are launched with programmatic serialization: this kernel may
-    // start while its predecessor is still draining.  The weights do not depend on the predecessor, so the first
-    // ring of weight tiles is requested right away; everything that reads the predecessor's output (tokens,
-    // token scales) or writes C comes after pdl_wait().
+    // start while its predecessor is still draining.  When the caller has vouched for the weights
+    // (B200_GEMM_INPUTS_READY: resident, not written by anything still in flight) the first ring of weight tiles is
+    // requested right away; otherwise the weights, like everything that may be the predecessor's output (tokens,
+    // token scales) and every write to C, come after pdl_wait().
     pdl_launch_dependents();
     const int first = nkb < STAGES ? nkb : STAGES;
+    auto request_weights = [&](int i) {
+        const uint32_t sw = smem_base + i * Cfg::STAGE_BYTES;
+        const uint32_t full = bar_full0 + i * 8;
+        mbar_arrive_expect_tx(full, Cfg::W_BYTES + Cfg::X_BYTES);
+        if constexpr (Cfg::BLAYOUT == BL_NK)
+            tma_load_3d(sw, &p.tmap_w, full, (kb0 + i) * BK, ni * BNW, b);
+        else
+            tma_load_4d(sw, &p.tmap_w, full, 0, ni * (BNW / 16), (kb0 + i) * (BK / 16), b);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full0 + s * 8, 1);
@@ -115,15 +126,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
-        for (int i = 0; i < first; ++i) {
-            const uint32_t sw = smem_base + i * Cfg::STAGE_BYTES;
-            const uint32_t full = bar_full0 + i * 8;
-            mbar_arrive_expect_tx(full, Cfg::W_BYTES + Cfg::X_BYTES);
-            if constexpr (Cfg::BLAYOUT == BL_NK)
-                tma_load_3d(sw, &p.tmap_w, full, (kb0 + i) * BK, ni * BNW, b);
-            else
-                tma_load_4d(sw, &p.tmap_w, full, 0, ni * (BNW / 16), (kb0 + i) * (BK / 16), b);
-        }
+        if (p.inputs_ready)
+            for (int i = 0; i < first; ++i) request_weights(i);
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -135,8 +139,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
     if (threadIdx.x == 0) {
-        for (int i = 0; i < first; ++i)
+        for (int i = 0; i < first; ++i) {
+            if (!p.inputs_ready) request_weights(i);
             tma_load_3d(smem_base + i * Cfg::STAGE_BYTES + Cfg::W_BYTES, &p.tmap_x, bar_full0 + i * 8, (kb0 + i) * BK, 0, b);
+        }
     }
 
     if (warp == 0) {

@@ -173,10 +173,17 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             // ------------------------------ TMA producer (both CTAs) ------------------------------
             uint32_t it = 0;
             bool ok = true;
+            int ready_b = -1;                         // last batch whose ready word has been seen
             const uint32_t leader_full0 = mapa_shared(bar_full0, 0);
             for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
                 int b, mi, ni;
                 tile_coords(p, t, b, mi, ni);
+                if (p.batch_ready && b != ready_b) {
+                    // this batch's activation slab may still be on its way (a copy or collective on another stream)
+                    if (!wait_ready_word(p.batch_ready + b, p.batch_epoch, abort_flag, p.status)) break;
+                    ready_b = b;
+                }
+                const int bq = p.b_shared ? 0 : b;    // batch coordinate of the weights
                 const int row_a = mi * (2 * BM) + static_cast<int>(cta) * BM;
                 const int row_b = ni * BN + static_cast<int>(cta) * BH;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
@@ -195,9 +202,9 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     const uint32_t full = leader_full0 + s * 8;
                     tma_load_3d_pair(sa, &p.tmap_a, full, kb * BK, row_a, b);
                     if constexpr (Cfg::BLAYOUT == BL_NK)
-                        tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, b);
+                        tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, bq);
                     else
-                        tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), b);
+                        tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), bq);
                     B200_TRACE_PROD(1);
                     if constexpr (MODE == MODE_MX) {
                         // scale atoms [batch][K/128][rows/128][512 B], addressed as rows of 256 bytes
@@ -316,6 +323,19 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
             int b, mi, ni;
             tile_coords(p, t, b, mi, ni);
+            // (first tile of this pair in batch b; recomputed from t so that no state stays live across the K loop)
+            if (MODE == MODE_BLOCK && p.batch_ready &&
+                (t < num_pairs || (t - num_pairs) / (p.tiles_m * p.tiles_n) != b)) {
+                // the A scales of this batch travel with its slab: they are read below, possibly long before the
+                // producer's first load of the tile, so the epilogue warps look at the ready word themselves
+                int seen = 1;
+                if (lane == 0) seen = wait_ready_word(p.batch_ready + b, p.batch_epoch, abort_flag, p.status) ? 1 : 0;
+                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+                if (!seen) {
+                    ok = false;
+                    break;
+                }
+            }
             const int row = mi * (2 * BM) + row_in_tile;
             const int row0 = row - lane;                       // output row of this warp's lane 0
             const int col_base = ni * BN + half * NCH;

@@ -43,6 +43,9 @@ struct GemmParams {
     int out_dtype;
     int c_tma;                   // block-scale pair kernels: finished tiles leave through TMA bulk stores
     int inputs_ready;            // pair kernels: operands do not depend on the previous kernel (see b200_gemm_flags)
+    int b_shared;                // pair kernels: every batch multiplies by the same B (B is read at batch coordinate 0)
+    int batch_epoch;             // pair kernels: value a batch's ready word must have reached (with batch_ready)
+    const int* batch_ready;      // pair kernels: one ready word per batch, or null
     int* status;
 };
 

@@ -1,6 +1,7 @@
 // Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk[.tensor]), tcgen05
 // (TMEM allocation, UMMA issue, commit, TMEM loads) and the bounded wait every kernel in
-// this library uses.  No instruction here carries a cluster-multicast qualifier.
+// this library uses.  No LOAD here carries a cluster-multicast qualifier (the one multicast instruction is the pair
+// kernels' tcgen05.commit, a completion signal that reads no memory).
 #pragma once
 
 #include <cuda.h>
@@ -19,6 +20,7 @@ enum : int {
     KSTAT_TIMEOUT_PEER  = 5,   // wait on the partner CTA of a pair expired
     KSTAT_TMEM_MISMATCH = 6,   // the two CTAs of a pair got different TMEM base addresses
     KSTAT_SELFTEST      = 7,   // the self-test's wait on a barrier nobody signals ran out, as it must
+    KSTAT_TIMEOUT_BATCH = 8,   // a batch's ready word did not reach the launch's epoch in time
 };
 
 // Wall-clock budget of one wait.  A wait that exceeds it records a status code, raises the
@@ -150,6 +152,27 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
             }
         }
     }
+}
+
+// Bounded wait for a ready word in global memory to reach `epoch` (B200_GEMM_BATCH_READY).  The word is written by
+// another agent -- a stream memory operation behind a copy or a collective, possibly a peer GPU -- after the data it
+// guards, hence the system-scope acquire; the proxy fence orders the TMA (async proxy) reads that follow.
+__device__ __forceinline__ bool wait_ready_word(const int* word, int epoch, volatile int* abort_flag, int* status) {
+    // bounded by iterations rather than by the clock (one counter instead of two 64-bit time stamps in the register
+    // budget of the epilogue warps): 4M polls with a sleep of at least 0.5 us between them, i.e. 2 s or somewhat more
+    for (int spins = 0; spins < (4 << 20); ++spins) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+        if (v >= epoch) {
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            return true;
+        }
+        if (*abort_flag) return false;
+        __nanosleep(500);
+    }
+    *abort_flag = 1;
+    if (status) atomicCAS(status, 0, static_cast<int>(KSTAT_TIMEOUT_BATCH));
+    return false;
 }
 
 // ---- TMA ----------------------------------------------------------------------------------

@@ -41,9 +41,13 @@ inline int64_t expected_scale_bytes(const b200_weight_desc& d) {
     }
 }
 
+// Largest N or K a header may state: keeps n * k and every scale-size product far inside int64_t, whatever a
+// corrupt or hostile file says (the fields come straight from disk).
+constexpr int64_t kWeightMaxDim = int64_t(1) << 31;
+
 inline int check_desc(const b200_weight_desc& d) {
     if (std::memcmp(d.magic, kWeightMagic, 8) != 0 || d.version != 1) return B200_ERR_BAD_ARG;
-    if (d.n <= 0 || d.k <= 0) return B200_ERR_BAD_ARG;
+    if (d.n <= 0 || d.k <= 0 || d.n > kWeightMaxDim || d.k > kWeightMaxDim) return B200_ERR_BAD_ARG;
     if (d.b_layout != B200_B_NK_ROWMAJOR && d.b_layout != B200_B_FLAT_16x16) return B200_ERR_BAD_ARG;
     if (d.b_layout == B200_B_FLAT_16x16 && (d.n % 16 != 0 || d.k % 16 != 0)) return B200_ERR_UNSUPPORTED;
     if (d.data_bytes != d.n * d.k) return B200_ERR_BAD_ARG;
@@ -58,6 +62,7 @@ inline int64_t scale_offset(const b200_weight_desc& d) { return 128 + (d.data_by
 inline int weight_file_write(const char* path, int32_t b_layout, int32_t scale_mode, int64_t n, int64_t k, const void* data,
                              const void* scales) {
     if (!path || !data) return B200_ERR_BAD_ARG;
+    if (n <= 0 || k <= 0 || n > kWeightMaxDim || k > kWeightMaxDim) return B200_ERR_BAD_ARG;
     b200_weight_desc d;
     std::memset(&d, 0, sizeof(d));
     std::memcpy(d.magic, kWeightMagic, 8);
@@ -92,7 +97,7 @@ inline int weight_file_stat(const char* path, b200_weight_desc* out) {
     b200_weight_desc d;
     const bool got = std::fread(&d, sizeof(d), 1, f) == 1;
     long long size = -1;
-    if (got && std::fseek(f, 0, SEEK_END) == 0) size = std::ftell(f);
+    if (got && fseeko(f, 0, SEEK_END) == 0) size = static_cast<long long>(ftello(f));
     std::fclose(f);
     if (!got) return B200_ERR_IO;
     int rc = check_desc(d);
@@ -112,7 +117,7 @@ inline int weight_file_read(const char* path, void* data, size_t data_capacity, 
     if (!f) return B200_ERR_IO;
     bool ok = std::fseek(f, 128, SEEK_SET) == 0;
     ok = ok && std::fread(data, 1, static_cast<size_t>(d.data_bytes), f) == static_cast<size_t>(d.data_bytes);
-    ok = ok && std::fseek(f, static_cast<long>(scale_offset(d)), SEEK_SET) == 0;
+    ok = ok && fseeko(f, static_cast<off_t>(scale_offset(d)), SEEK_SET) == 0;
     ok = ok && (d.scale_bytes == 0 || std::fread(scales, 1, static_cast<size_t>(d.scale_bytes), f) == static_cast<size_t>(d.scale_bytes));
     std::fclose(f);
     if (!ok) return B200_ERR_IO;

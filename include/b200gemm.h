@@ -73,23 +73,45 @@ typedef struct b200_gemm_args {
     int32_t out_dtype;            /* b200_out_dtype   */
     int32_t tile_hint;            /* b200_tile_hint   */
     int32_t flags;                /* b200_gemm_flags, 0 for the reference's behaviour */
-    int32_t reserved;             /* 0 */
+    int32_t batch_epoch;          /* B200_GEMM_BATCH_READY: the value a batch's ready word must have reached   */
+    const int32_t* ptr_batch_ready; /* B200_GEMM_BATCH_READY: device int32 [batch]; null otherwise              */
 } b200_gemm_args;
 
 /* Launches on one stream are chained with programmatic dependent launch: a GEMM's prologue (barrier set-up, TMEM
  * allocation) runs while the previous kernel drains, and by default everything else waits for the previous kernel
- * to complete.  B200_GEMM_INPUTS_READY is the caller's promise that A, B and the scales of THIS call are not
- * written by work still in flight on the stream (for instance consecutive GEMMs of independent requests, or
- * weights and activations prepared earlier): the kernel then starts loading and multiplying at once -- on the SMs
- * the previous launch no longer uses, e.g. during its last, partly filled wave of tiles -- and only its writes to C
- * wait for the previous kernel.  Honoured by the 2-CTA tile kernels; other paths ignore it.                    */
-enum b200_gemm_flags { B200_GEMM_INPUTS_READY = 1 };
+ * to complete.
+ * B200_GEMM_INPUTS_READY is the caller's promise that A, B and the scales of THIS call are not written by work
+ * still in flight on the stream (for instance consecutive GEMMs of independent requests, or weights and
+ * activations prepared earlier).  The 2-CTA tile kernels then start loading and multiplying at once -- on the SMs
+ * the previous launch no longer uses, e.g. during its last, partly filled wave of tiles -- and only their writes to
+ * C wait for the previous kernel.  The skinny-M kernel requests its first ring of WEIGHT tiles before it waits for
+ * the previous kernel only when this flag is set (without it a weight written by the previous kernel -- a shuffle,
+ * a quantiser, a copy -- is read only after that kernel has completed).  The single-CTA tile kernels ignore it.
+ * B200_GEMM_BATCH_READY turns `batch` into a sequence of activation slabs that may still be arriving while the
+ * kernel runs: before anything of batch b's A or SFA is read, the kernel waits until ptr_batch_ready[b] >=
+ * batch_epoch (a bounded wait: after 2 s the launch gives up and b200_last_status() reports 8).  Whoever delivers
+ * the slab -- a copy or a collective on another stream, a peer GPU -- writes the word after the slab's last byte,
+ * e.g. with b200_flag_write on the delivering stream.  B, SFB and C are not covered: B must be resident, and C is
+ * ordered like any other launch.  Words only grow (use a step counter as epoch), so nothing is ever cleared.
+ * Implies that A does not depend on the previous kernel of the stream (the ready words order it instead).
+ * Only the 2-CTA tile kernels implement it: M > 128 per batch and scale mode NONE, TENSOR or BLOCK, else
+ * B200_ERR_UNSUPPORTED.
+ * A batched problem may share one B: stride_b_batch == 0 (and stride_sfb_batch == 0) makes every batch multiply
+ * by the same weights (2-CTA tile kernels and b200_gemm_a8w8_simple).                                            */
+enum b200_gemm_flags { B200_GEMM_INPUTS_READY = 1, B200_GEMM_BATCH_READY = 2 };
 
 /* Replaces the launches `gemm_a8w8_kernel<Traits><<<grid,block>>>(kargs)` (gemm_a8w8_8wave.cc:738),
  * `gemm_a8w8_blockscale_kernel<GemmTraits><<<grid,block>>>(kargs)` (gemm_a8w8_blockscale_host.cc:257)
  * and `flatmm_kernel<Traits><<<grid,block>>>(kargs)` (flatmm_a8w8_gfx950.cc:780).  Asynchronous on
  * `cuda_stream` (a cudaStream_t, 0 = default stream); buffers are caller-owned device memory.           */
 int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream);
+/* Rules of the skinny-M path (M <= 64) of b200_gemm_a8w8.  When a problem has fewer 128-row weight panels than the
+ * GPU has SMs the kernel splits K and needs an fp32 workspace.  The library keeps one workspace per (device,
+ * stream) -- launches on different streams never share one -- allocates it with cudaMalloc on first use or when a
+ * larger one is needed, and never frees or moves a workspace that a launch has been given (b200_release frees them
+ * all).  So: make the first split-K call of a stream, at the largest size it will see, before capturing that stream
+ * into a CUDA graph (an allocation cannot happen inside a capture, and a captured launch keeps the pointer it was
+ * given); and do not call b200_release while captured graphs that contain these launches are still replayed.      */
 
 /* Validates `args` exactly as b200_gemm_a8w8 would, without touching the GPU. Also reports the tile
  * configuration the launcher would pick (a b200_tile_hint value) when `chosen_tile` is not null.        */
@@ -100,7 +122,11 @@ int b200_gemm_check(const b200_gemm_args* args, int32_t* chosen_tile);
  * checker for problem sizes the CPU loops cannot finish.  MX scales are read in the relayouted form.     */
 int b200_gemm_a8w8_simple(const b200_gemm_args* args, void* cuda_stream);
 
-/* Whole reference main() data path with HOST buffers (hipMemcpy H2D -> launch -> hipMemcpy D2H,
+/* Not re-entrant per device: the staging buffers, the copy stream and its events are shared, so concurrent callers on
+ * one device are serialised by a per-device lock inside the call.  Arguments are validated (and byte sizes checked for
+ * overflow) before anything is allocated or queued.  After the final synchronisation the device status word is read:
+ * a launch that gave up makes the call return B200_ERR_DEVICE_TIMEOUT instead of delivering a wrong C.
+ * Whole reference main() data path with HOST buffers (hipMemcpy H2D -> launch -> hipMemcpy D2H,
  * gemm_a8w8_blockscale_host.cc:212-226,257,262): copies the operands in `args` (host pointers) to
  * device buffers owned by the library, runs the GEMM and copies C back; returns after the copy-back.
  * Device buffers are cached per device and grown on demand; b200_release() frees them.  Single-batch problems
@@ -178,7 +204,8 @@ size_t b200_mx_sf_bytes(int64_t rows, int64_t k);
 /* A pre-quantised, optionally pre-shuffled B operand with its scales on disk, so that a run does not repeat the
  * host-side layout pass the reference performs at every start (opus_fmm/flatmm_a8w8_gfx950.cc:736-742).  The
  * reference has no file format; this one is: 128-byte header below, N*K operand bytes, padding to 64, scales.
- * Little-endian.  checksum = FNV-1a/64 over operand bytes then scale bytes.                                 */
+ * Little-endian.  checksum = FNV-1a/64 over operand bytes then scale bytes.  8-bit (e4m3) operands only: the header
+ * has no element-size field, so the bf16 siblings' weights are not storable.  N and K are limited to 2^31.       */
 typedef struct b200_weight_desc {
     char magic[8];            /* "B200WGT1" */
     int32_t version;          /* 1 */
@@ -211,10 +238,20 @@ int b200_membw_copy(const void* src, void* dst, size_t bytes, void* cuda_stream)
 void b200_fill_uniform(float* host_out, size_t count, uint64_t seed, uint32_t tensor_id, float lo, float hi);
 void b200_fill_normal(float* host_out, size_t count, uint64_t seed, uint32_t tensor_id);
 
+/* ---- stream-ordered flag write --------------------------------------------------------------------- */
+/* Writes `value` to the device word `flag` when everything queued on `cuda_stream` before this call has completed
+ * (a stream memory operation: no kernel, no SM).  The producer side of B200_GEMM_BATCH_READY: queue it behind the
+ * copy or collective that delivers a slab.  No counterpart in the reference (its kernels never wait for data).    */
+int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream);
+
 /* ---- status / housekeeping --------------------------------------------------------------------- */
-/* Device status word of the current device: 0, or the code of the first bounded wait that expired
- * since the last call (which also clears it).  Synchronises the device.                                  */
+/* Device status word of the current device: 0, or the code of the first bounded wait that expired (1-5, 8), of a
+ * pair launch whose two CTAs disagreed on their tensor-memory address (6: that launch computed nothing) or of the
+ * self-test (7) since the last call, which also clears it.  Synchronises the device.                         */
 int b200_last_status(void);
+/* The same word without synchronising and without clearing it: what has been recorded by kernels that have
+ * already finished.  Cheap enough to poll between steps of a serving loop.                                   */
+int b200_peek_status(void);
 /* Self-test of the failure path: a one-block kernel waits, with a budget of `budget_us` (100..100000), on a barrier
  * that nothing signals (polling != 0: the test_wait flavour).  Returns B200_OK when both waiting threads gave up;
  * afterwards b200_last_status() reports 7 (the self-test's code) once, and the context stays usable.  No part of

@@ -184,3 +184,66 @@ def test_sibling_entry_argument_checks(native):
 
     assert native.b200_membw_read(0x1000, 20, 0x2000, None) == L.ERR_UNSUPPORTED          # bytes % 16
     assert native.b200_membw_copy(0x1000, None, 32, None) == L.ERR_BAD_ARG
+
+
+def test_batch_ready_and_shared_b_validation(native):
+    """B200_GEMM_BATCH_READY (slabs that are still arriving) and a B shared by all batches: 2-CTA tile kernels only."""
+    from gcnasm_b200 import _lib as L
+
+    tile = C.c_int32(0)
+    chk = lambda a: native.b200_gemm_check(C.byref(a), C.byref(tile))
+    bs = dict(scale_mode=L.SCALE_BLOCK, ptr_sfa=0x4000, ptr_sfb=0x5000, stride_sfa=2048, stride_sfb=64)
+    big = dict(m=2048, n=7168, k=8192, batch=8, stride_a=8192, stride_b=8192, stride_c=7168,
+               stride_a_batch=2048 * 8192 + 64 * 2048 * 4, stride_b_batch=0, stride_c_batch=2048 * 7168,
+               stride_sfa_batch=(2048 * 8192 + 64 * 2048 * 4) // 4, stride_sfb_batch=0)
+    pair_tiles = (L.TILE_PAIR_256x256, L.TILE_PAIR_256x224, L.TILE_PAIR_256x192, L.TILE_PAIR_256x128)
+    # shared B without ready words
+    assert chk(_args(**big, **bs)) == L.OK and tile.value in pair_tiles
+    # ready words
+    rdy = dict(flags=L.GEMM_BATCH_READY, ptr_batch_ready=0x6000, batch_epoch=3)
+    assert chk(_args(**big, **bs, **rdy)) == L.OK and tile.value in pair_tiles
+    assert chk(_args(**big, **bs, flags=L.GEMM_BATCH_READY)) == L.ERR_BAD_ARG                       # no ready words given
+    assert chk(_args(**{**big, "m": 128}, **bs, **rdy)) == L.ERR_UNSUPPORTED                          # needs the pair tiles
+    assert chk(_args(**big, **bs, **rdy, tile_hint=L.TILE_128x256)) == L.ERR_UNSUPPORTED
+    assert chk(_args(**big, **bs, **rdy, tile_hint=L.TILE_PAIR_256x256)) == L.OK
+    assert chk(_args(**big, **{**bs, "scale_mode": L.SCALE_MX}, **rdy)) == L.ERR_UNSUPPORTED
+    assert chk(_args(**{**big, "stride_sfb_batch": 448}, **bs)) == L.ERR_BAD_ARG                      # B shared, SFB not
+    # small shapes keep their single-CTA tiles when nothing asks for the pair kernels
+    assert chk(_args(m=256, n=512, k=1024, batch=2)) == L.OK
+    assert native.b200_flag_write(None, 1, None) == L.ERR_BAD_ARG
+    assert native.b200_flag_write(0x1002, 1, None) == L.ERR_BAD_ARG
+
+
+def test_host_entry_rejects_bad_arguments_before_touching_the_device(native):
+    from gcnasm_b200 import _lib as L
+
+    assert native.b200_gemm_a8w8_host(None, None) == L.ERR_BAD_ARG
+    assert native.b200_gemm_a8w8_host(C.byref(_args(ptr_c=0)), None) == L.ERR_BAD_ARG
+    assert native.b200_gemm_a8w8_host(C.byref(_args(flags=L.GEMM_BATCH_READY, ptr_batch_ready=0x100)), None) == L.ERR_UNSUPPORTED
+
+
+class _FakeTensor:
+    """Just enough of a tensor for the device check (no GPU needed)."""
+
+    def __init__(self, index):
+        import torch
+
+        self.is_cuda = True
+        self.device = torch.device("cuda", index)
+
+
+def test_operands_must_share_the_current_device(monkeypatch):
+    import torch
+
+    from gcnasm_b200 import api
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    assert api._same_device(_FakeTensor(0), None, _FakeTensor(0)) == torch.device("cuda", 0)
+    with pytest.raises(ValueError, match="different devices"):
+        api._same_device(_FakeTensor(0), _FakeTensor(1))
+    with pytest.raises(ValueError, match="current device"):
+        api._same_device(_FakeTensor(1), _FakeTensor(1))
+    cpu = _FakeTensor(0)
+    cpu.is_cuda = False
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        api._same_device(cpu)

@@ -120,3 +120,23 @@ def test_header_layout_is_fixed(tmp_path, O):
         h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
     assert int(np.frombuffer(raw, np.uint64, 1, 56)[0]) == h
     assert C.sizeof(weights.WeightDesc) == 128
+
+
+def test_overflowing_header_is_rejected(tmp_path, O):
+    """A header whose N and K would overflow the size arithmetic (corrupt or hostile file) is a bad argument."""
+    n, k = 128, 128
+    q, sfb = _case(O, n, k, 36)
+    path = str(tmp_path / "w.b2w")
+    weights.save(path, q, sfb, n, k, scale_mode=L.SCALE_BLOCK)
+    blob = bytearray(open(path, "rb").read())
+    for nn, kk in ((1 << 62, 1 << 62), ((1 << 31) + 128, 128), (3 << 40, 3 << 22)):
+        bad = bytearray(blob)
+        bad[24:40] = np.array([nn, kk], np.int64).tobytes()
+        bad[40:48] = np.array([(nn * kk) & 0x7FFFFFFFFFFFFFFF], np.int64).tobytes()      # whatever the product wraps to
+        open(tmp_path / "huge.b2w", "wb").write(bad)
+        with pytest.raises(B200Error) as e:
+            weights.stat(str(tmp_path / "huge.b2w"))
+        assert e.value.code == L.ERR_BAD_ARG
+    rc = L.lib().b200_weight_file_write(str(tmp_path / "x.b2w").encode(), L.B_NK_ROWMAJOR, L.SCALE_NONE, 1 << 40, 1 << 40,
+                                        q.ctypes.data, None)
+    assert rc == L.ERR_BAD_ARG
