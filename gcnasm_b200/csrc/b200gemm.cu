@@ -65,10 +65,6 @@ EncodeTiledFn g_encode = nullptr;
 typedef CUresult (*StreamWriteValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
 StreamWriteValue32Fn g_write_value32 = nullptr;     // null when the driver does not offer stream memory operations
 
-__global__ void flag_write_kernel(int* flag, int value) {
-    *flag = value;
-    __threadfence_system();
-}
 
 int device_state(DeviceState** out) {
     int dev = 0;
@@ -1230,9 +1226,29 @@ int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream) {
         g_last_cuda = 100000 + static_cast<int>(r);
         return B200_ERR_CUDA;
     }
-    flag_write_kernel<<<1, 1, 0, st>>>(flag, value);         // drivers without stream memory operations
-    CU_TRY(cudaGetLastError());
-    g_launches.fetch_add(1);
+    // A driver without stream memory operations: a one-thread kernel could do the write, but it would need an SM,
+    // and the consumer of these words is a persistent GEMM that may hold every SM while it waits for them.
+    return B200_ERR_UNSUPPORTED;
+}
+size_t b200_slab_bytes(int64_t slab_rows, int64_t k) {
+    if (slab_rows <= 0 || k <= 0 || k % 128 != 0 || slab_rows % 4 != 0) return 0;
+    return static_cast<size_t>(slab_rows) * static_cast<size_t>(k) + 4 * static_cast<size_t>(k / 128) * static_cast<size_t>(slab_rows);
+}
+int b200_slab_upload(const void* host_a, const float* host_sfa, void* dev_slabs, int64_t m, int64_t k, int64_t slab_rows,
+                     int64_t slab, void* cuda_stream) {
+    if (!host_a || !host_sfa || !dev_slabs || m <= 0 || slab < 0) return B200_ERR_BAD_ARG;
+    const size_t bytes = b200_slab_bytes(slab_rows, k);
+    if (bytes == 0) return B200_ERR_UNSUPPORTED;
+    if (m % slab_rows != 0 || (slab + 1) * slab_rows > m) return B200_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    uint8_t* dst = static_cast<uint8_t*>(dev_slabs) + static_cast<size_t>(slab) * bytes;
+    const size_t a_bytes = static_cast<size_t>(slab_rows) * static_cast<size_t>(k);
+    CU_TRY(cudaMemcpyAsync(dst, static_cast<const uint8_t*>(host_a) + static_cast<size_t>(slab) * a_bytes, a_bytes,
+                           cudaMemcpyHostToDevice, st));
+    // the slab's columns of every K group: K/128 rows of slab_rows floats, source pitch M floats
+    CU_TRY(cudaMemcpy2DAsync(dst + a_bytes, static_cast<size_t>(slab_rows) * 4, host_sfa + slab * slab_rows,
+                             static_cast<size_t>(m) * 4, static_cast<size_t>(slab_rows) * 4, static_cast<size_t>(k / 128),
+                             cudaMemcpyHostToDevice, st));
     return B200_OK;
 }
 int b200_selftest_bounded_wait(int64_t budget_us, int32_t polling, void* cuda_stream) {

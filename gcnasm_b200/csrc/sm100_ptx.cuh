@@ -159,8 +159,8 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
 // guards, hence the system-scope acquire; the proxy fence orders the TMA (async proxy) reads that follow.
 __device__ __forceinline__ bool wait_ready_word(const int* word, int epoch, volatile int* abort_flag, int* status) {
     // bounded by iterations rather than by the clock (one counter instead of two 64-bit time stamps in the register
-    // budget of the epilogue warps): 4M polls with a sleep of at least 0.5 us between them, i.e. 2 s or somewhat more
-    for (int spins = 0; spins < (4 << 20); ++spins) {
+    // budget of the epilogue warps): 1M polls, each a system-scope load plus a sleep of 0.5-1 us, i.e. 2 s or so
+    for (int spins = 0; spins < (1 << 20); ++spins) {
         int v;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
         if (v >= epoch) {

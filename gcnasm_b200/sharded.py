@@ -5,10 +5,23 @@ keeps ``B[r*N/R:(r+1)*N/R, :]`` with its 128x128 scale blocks and produces ``C[:
 exchange is the activation: A and its 1x128 scales are broadcast from the root over NCCL once per call.
 The result stays N-sharded; an all-gather into ``[R, M, N/R]`` is optional.  One process per GPU,
 ``torch.distributed`` supplies the process group (NCCL on GPUs; gloo in the CPU tests of the host logic).
+
+Two ways to run a call:
+
+* ``op(a, sfa)`` / ``op.forward_bf16(x, ...)``: one broadcast of the whole activation, then the GEMM.
+* ``op.step(i, ...)`` (``post`` + ``run``): the activation is cut into M slabs (``b200_slab_bytes``: each slab is one
+  contiguous ``[rows x K bytes | K/128 x rows scales]`` piece).  The slabs are delivered one after the other on a
+  side stream -- root: quantise or upload the slab; all: broadcast it; then a stream-ordered write of the slab's
+  ready word -- while ONE persistent GEMM launch on the main stream consumes slab s as batch s as soon as its
+  ready word shows the step's epoch (``B200_GEMM_BATCH_READY``).  Only the first slab's delivery is exposed, and
+  with ``nbuf`` >= 2 activation buffers the delivery of step i+1 runs entirely behind the GEMM of step i.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+import contextlib
+import os
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -24,11 +37,53 @@ def shard_bounds(n: int, world: int, rank: int, align: int = 128) -> Tuple[int, 
     return rank * per, (rank + 1) * per
 
 
+def pick_slab_rows(m: int, want: int = 2048) -> int:
+    """Rows per activation slab: the largest multiple of 256 (the GEMM's row tile) that divides M and is at most
+    ``want``; M itself when there is none (one slab)."""
+    best = 0
+    for rows in range(256, min(m, want) + 1, 256):
+        if m % rows == 0:
+            best = rows
+    return best or m
+
+
+def slab_bytes(rows: int, k: int) -> int:
+    """Bytes of one slab: rows x K e4m3 bytes followed by K/128 x rows fp32 scales (``b200_slab_bytes``)."""
+    if k % 128 != 0 or rows % 4 != 0:
+        raise ValueError("slabs need K % 128 == 0 and rows % 4 == 0")
+    return rows * k + 4 * (k // 128) * rows
+
+
+def configure_overlap(world: int, sm_count: int = 148, comm_sms: int = 4) -> None:
+    """Call before the process group is created.  The GEMM kernels are persistent -- one CTA per SM until the last
+    tile -- so a collective that is to run BESIDE a GEMM needs SMs the GEMM does not occupy: the GEMM grid is capped at
+    ``sm_count - comm_sms`` SMs and NCCL is held to ``comm_sms`` channels (one CTA each, no CTA clusters, so that any
+    free SM will do).  Existing settings of the variables win."""
+    if world <= 1:
+        return
+    os.environ.setdefault("NCCL_MAX_NCHANNELS", str(comm_sms))
+    os.environ.setdefault("NCCL_MIN_NCHANNELS", str(comm_sms))
+    os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "0")
+    os.environ.setdefault("B200GEMM_MAX_SMS", str(sm_count - comm_sms))
+
+
+@dataclass
+class SlabPlan:
+    m: int
+    k: int
+    rows: int            # rows per slab
+    slabs: int
+    bytes_per_slab: int
+    nbuf: int
+
+
 class ColumnShardedGemm:
     """Holds one rank's weight shard; ``__call__`` broadcasts the activation and runs the local GEMM."""
 
     def __init__(self, b_shard: torch.Tensor, sfb_shard: torch.Tensor, n_total: int, group=None,
-                 gemm_fn: Optional[Callable] = None, out_dtype=torch.bfloat16, quant_fn: Optional[Callable] = None):
+                 gemm_fn: Optional[Callable] = None, out_dtype=torch.bfloat16, quant_fn: Optional[Callable] = None,
+                 slab_gemm_fn: Optional[Callable] = None, flag_fn: Optional[Callable] = None,
+                 upload_fn: Optional[Callable] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -50,7 +105,34 @@ class ColumnShardedGemm:
 
                 api.quantize_act_bf16_1x128(x, q=q, sfa=sfa)
         self.quant_fn = quant_fn
+        # the three device-specific pieces of the slab path (replaced by host stand-ins in the CPU tests of the logic)
+        if slab_gemm_fn is None:
+            def slab_gemm_fn(a3, b, sfa3, sfb, out3, ready, epoch):
+                from . import api
+
+                api.gemm_a8w8_blockscale(a3, b, sfa3, sfb, out=out3, batch_ready=ready, batch_epoch=epoch)
+        self.slab_gemm_fn = slab_gemm_fn
+        if flag_fn is None:
+            def flag_fn(ready, index, value):
+                from . import api
+
+                api.flag_write(ready, index, value)
+        self.flag_fn = flag_fn
+        if upload_fn is None:
+            def upload_fn(a_host, sfa_host, buf, m, k, rows, slab):
+                from . import _lib as L
+
+                L.check(L.lib().b200_slab_upload(a_host.data_ptr(), sfa_host.data_ptr(), buf.data_ptr(), m, k, rows, slab,
+                                                 torch.cuda.current_stream().cuda_stream), "b200_slab_upload")
+        self.upload_fn = upload_fn
         self._act_buf = None
+        self._plan: Optional[SlabPlan] = None
+        self._bufs: List[torch.Tensor] = []
+        self._ready: List[torch.Tensor] = []
+        self._gemm_done: List[Optional[object]] = []
+        self._posted: List[Optional[object]] = []
+        self._comm = None
+        self.overlap = True
 
     def check_agreement(self, m: int, k: int) -> None:
         """Host-side guard before a collective: every rank must be about to run the same (M, K).  A rank that
@@ -79,7 +161,11 @@ class ColumnShardedGemm:
         self.gemm_fn(a, self.b, sfa, self.sfb, out)
         if not gather:
             return out
-        full = torch.empty((self.world, m, self.n1 - self.n0), dtype=out.dtype, device=out.device)
+        return self.gather(out)
+
+    def gather(self, out: torch.Tensor) -> torch.Tensor:
+        """All-gather of the shards into ``[R, M, N/R]`` (rank r's columns are ``full[r]``)."""
+        full = torch.empty((self.world,) + tuple(out.shape), dtype=out.dtype, device=out.device)
         if self.world > 1:
             dist.all_gather(list(full.unbind(0)), out.contiguous(), group=self.group)
         else:
@@ -113,3 +199,142 @@ class ColumnShardedGemm:
         if self.world > 1:
             dist.broadcast(buf, src=root, group=self.group)
         return self(a, sfa, root=root, out=out, gather=gather, broadcast=False)
+
+    # ------------------------------------------------------------------------------------------------------
+    # slab pipeline
+    # ------------------------------------------------------------------------------------------------------
+    def plan_slabs(self, m: int, k: int, device, slab_rows: Optional[int] = None, nbuf: int = 2) -> SlabPlan:
+        """Allocates ``nbuf`` activation buffers in the slab layout and their ready words (one int32 per slab and
+        buffer, never cleared: a step's epoch is its number + 1, and words only grow)."""
+        rows = slab_rows or pick_slab_rows(m)
+        if m % rows != 0:
+            raise ValueError(f"M={m} is not a whole number of {rows}-row slabs")
+        plan = SlabPlan(m, k, rows, m // rows, slab_bytes(rows, k), nbuf)
+        device = torch.device(device)
+        if self._plan != plan or not self._bufs or self._bufs[0].device != device:
+            self._plan = plan
+            self._bufs = [torch.empty(plan.slabs * plan.bytes_per_slab, dtype=torch.uint8, device=device) for _ in range(nbuf)]
+            self._ready = [torch.zeros(plan.slabs, dtype=torch.int32, device=device) for _ in range(nbuf)]
+            self._gemm_done = [None] * nbuf
+            self._posted = [None] * nbuf
+            self._comm = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+            # may a collective run BESIDE a GEMM that is waiting for it?  Only when the GEMM grid leaves SMs free
+            # (configure_overlap); a single rank has no collective to starve
+            self.overlap = True
+            if device.type == "cuda" and self.world > 1:
+                from . import _lib as L
+
+                with torch.cuda.device(device):
+                    self.overlap = L.lib().b200_sm_count() < torch.cuda.get_device_properties(device).multi_processor_count
+        return plan
+
+    def slab_views(self, buf_index: int):
+        """(bytes [slabs, bytes_per_slab], A [slabs, rows, K], SFA [slabs, K/128, rows]) over activation buffer ``buf_index``."""
+        p = self._plan
+        buf = self._bufs[buf_index]
+        kg = p.k // 128
+        a3 = torch.as_strided(buf, (p.slabs, p.rows, p.k), (p.bytes_per_slab, p.k, 1))
+        sfa3 = torch.as_strided(buf.view(torch.float32), (p.slabs, kg, p.rows), (p.bytes_per_slab // 4, p.rows, 1),
+                                storage_offset=p.rows * p.k // 4)
+        return buf.view(p.slabs, p.bytes_per_slab), a3, sfa3
+
+    def _on_comm(self):
+        return torch.cuda.stream(self._comm) if self._comm is not None else contextlib.nullcontext()
+
+    def post(self, step: int, *, a: Optional[torch.Tensor] = None, sfa: Optional[torch.Tensor] = None,
+             x_bf16: Optional[torch.Tensor] = None, prefilled: bool = False, root: int = 0) -> None:
+        """Delivers the activation of ``step`` slab by slab on the side stream (returns at once on a GPU).
+
+        The root's source -- exactly one of: ``x_bf16`` [M,K] (device; quantised slab by slab by the fused quantiser),
+        ``a`` + ``sfa`` on the device (already quantised, reference layouts: copied into the slabs), ``a`` + ``sfa``
+        in pinned HOST memory (uploaded slab by slab), or ``prefilled=True`` (the caller has written the slabs of
+        buffer ``step % nbuf`` itself through ``slab_views``, on the current stream) -- is ignored on the other ranks.
+        Every slab is then broadcast, and its ready word is written behind the broadcast."""
+        p = self._plan
+        if p is None:
+            raise RuntimeError("plan_slabs() first")
+        buf_index = step % p.nbuf
+        epoch = step + 1
+        raw, a3, sfa3 = self.slab_views(buf_index)
+        ready = self._ready[buf_index]
+        is_root = self.rank == root
+        if is_root and not prefilled and x_bf16 is None and (a is None or sfa is None):
+            raise ValueError("the root needs the activation: x_bf16, a and sfa, or prefilled slabs")
+        on_gpu = self._comm is not None
+        from_host = is_root and not prefilled and x_bf16 is None and a.device.type == "cpu" and on_gpu
+        filled: List[Optional[object]] = [None] * p.slabs
+        if on_gpu and self._gemm_done[buf_index] is not None:
+            # the buffer was last read by the GEMM of step - nbuf
+            torch.cuda.current_stream().wait_event(self._gemm_done[buf_index])
+            self._comm.wait_event(self._gemm_done[buf_index])
+        if is_root and prefilled and on_gpu:
+            self._comm.wait_stream(torch.cuda.current_stream())
+        if is_root and not from_host and not prefilled:
+            # Slabs that a KERNEL produces (the fused quantiser, a device copy) are filled on the caller's stream, ahead
+            # of the GEMM launch that will consume them: a persistent GEMM that is already spinning on a ready word
+            # occupies its SMs until the word arrives, and a producer kernel queued behind it on another stream could
+            # wait for an SM forever.  Copies by the copy engines and NCCL (which has SMs set aside, see
+            # configure_overlap) have no such dependency and run on the side stream.
+            for s in range(p.slabs):
+                r0, r1 = s * p.rows, (s + 1) * p.rows
+                if x_bf16 is not None:
+                    self.quant_fn(x_bf16[r0:r1], a3[s], sfa3[s])
+                else:
+                    a3[s].copy_(a[r0:r1], non_blocking=True)
+                    sfa3[s].copy_(sfa[:, r0:r1], non_blocking=True)
+                if on_gpu:
+                    filled[s] = torch.cuda.Event()
+                    filled[s].record()
+        with self._on_comm():
+            for s in range(p.slabs):
+                if from_host:
+                    self.upload_fn(a, sfa, self._bufs[buf_index], p.m, p.k, p.rows, s)
+                if filled[s] is not None:
+                    self._comm.wait_event(filled[s])
+                if self.world > 1:
+                    dist.broadcast(raw[s], src=root, group=self.group)
+                self.flag_fn(ready, s, epoch)
+            if on_gpu and not self.overlap:
+                self._posted[buf_index] = torch.cuda.Event()
+                self._posted[buf_index].record()
+
+    def run(self, step: int, out: torch.Tensor) -> torch.Tensor:
+        """One GEMM launch over all slabs of ``step`` (slab s = batch s, the shard's B shared by all batches); the
+        kernel itself waits for each slab's ready word.  ``out``: ``[M, N/R]``, contiguous."""
+        p = self._plan
+        buf_index = step % p.nbuf
+        _, a3, sfa3 = self.slab_views(buf_index)
+        n = self.n1 - self.n0
+        if tuple(out.shape) != (p.m, n) or not out.is_contiguous():
+            raise ValueError("out must be a contiguous [M, N/R] tensor")
+        if self._comm is not None and not self.overlap and self._posted[buf_index] is not None:
+            # no SMs are set aside for the collective: a GEMM spinning on a ready word could starve the very
+            # broadcast it waits for, so the launch is ordered behind the whole delivery instead
+            torch.cuda.current_stream().wait_event(self._posted[buf_index])
+        self.slab_gemm_fn(a3, self.b, sfa3, self.sfb, out.view(p.slabs, p.rows, n), self._ready[buf_index], step + 1)
+        if self._comm is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._gemm_done[buf_index] = ev
+        return out
+
+    def step(self, step: int, out: torch.Tensor, **source) -> torch.Tensor:
+        """``post(step, **source)`` then ``run(step, out)``."""
+        self.post(step, **source)
+        return self.run(step, out)
+
+    def check_rows(self, step: int, out: torch.Tensor, row0: int, rows: int = 128):
+        """Recomputes ``rows`` output rows starting at ``row0`` (inside one slab) of this rank's shard with the
+        one-thread-per-output checker kernel (the device mirror of the reference's host loop) from the activation
+        buffer of ``step``, and returns (max|err|, max|ref|) against ``out``."""
+        from . import api
+
+        p = self._plan
+        _, a3, sfa3 = self.slab_views(step % p.nbuf)
+        s, r = divmod(row0, p.rows)
+        if r + rows > p.rows:
+            raise ValueError("the checked rows must lie inside one slab")
+        ref = api.gemm_a8w8_blockscale(a3[s, r:r + rows], self.b, sfa3[s][:, r:r + rows], self.sfb, out_dtype=torch.float32,
+                                       simple=True)
+        got = out[row0:row0 + rows].float()
+        return float((got - ref).abs().max().item()), float(ref.abs().max().item())

@@ -89,7 +89,7 @@ typedef struct b200_gemm_args {
  * a quantiser, a copy -- is read only after that kernel has completed).  The single-CTA tile kernels ignore it.
  * B200_GEMM_BATCH_READY turns `batch` into a sequence of activation slabs that may still be arriving while the
  * kernel runs: before anything of batch b's A or SFA is read, the kernel waits until ptr_batch_ready[b] >=
- * batch_epoch (a bounded wait: after 2 s the launch gives up and b200_last_status() reports 8).  Whoever delivers
+ * batch_epoch (a bounded wait: after about 2 s the launch gives up and b200_last_status() reports 8).  Whoever delivers
  * the slab -- a copy or a collective on another stream, a peer GPU -- writes the word after the slab's last byte,
  * e.g. with b200_flag_write on the delivering stream.  B, SFB and C are not covered: B must be resident, and C is
  * ordered like any other launch.  Words only grow (use a step counter as epoch), so nothing is ever cleared.
@@ -241,8 +241,24 @@ void b200_fill_normal(float* host_out, size_t count, uint64_t seed, uint32_t ten
 /* ---- stream-ordered flag write --------------------------------------------------------------------- */
 /* Writes `value` to the device word `flag` when everything queued on `cuda_stream` before this call has completed
  * (a stream memory operation: no kernel, no SM).  The producer side of B200_GEMM_BATCH_READY: queue it behind the
- * copy or collective that delivers a slab.  No counterpart in the reference (its kernels never wait for data).    */
+ * copy or collective that delivers a slab.  B200_ERR_UNSUPPORTED on a driver without stream memory operations.
+ * No counterpart in the reference (its kernels never wait for data).                                             */
 int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream);
+
+/* ---- activation slabs ---------------------------------------------------------------------------------- */
+/* The layout in which the N-sharded mode moves a block-scale activation between GPUs and feeds it to a batched GEMM
+ * (B200_GEMM_BATCH_READY): the M rows are cut into slabs of `slab_rows`, and slab s is ONE contiguous piece
+ *     [ slab_rows x K e4m3 bytes | (K/128) x slab_rows fp32 scales ]
+ * i.e. a complete (A, SFA) pair in the reference's layouts (block_scale_gemm/README.md:21,28) for its rows, so that a
+ * slab travels as a single copy or collective and the GEMM addresses slab s as batch s (stride_a_batch =
+ * b200_slab_bytes, ptr_sfa = base + slab_rows * K, stride_sfa = slab_rows, stride_sfa_batch = b200_slab_bytes / 4).
+ * No counterpart in the reference (single GPU, operands uploaded whole).  K % 128 == 0, slab_rows % 4 == 0.        */
+size_t b200_slab_bytes(int64_t slab_rows, int64_t k);
+/* Queues on `cuda_stream` the upload of rows [slab * slab_rows, +slab_rows) of a HOST activation in the reference's
+ * layouts -- A [M][K] bytes, SFA fp32 [K/128][M] -- into slab `slab` of a device buffer in the slab layout: one
+ * contiguous copy for the bytes, one pitched copy for the scale columns.  Pinned host memory makes it asynchronous.  */
+int b200_slab_upload(const void* host_a, const float* host_sfa, void* dev_slabs, int64_t m, int64_t k, int64_t slab_rows,
+                     int64_t slab, void* cuda_stream);
 
 /* ---- status / housekeeping --------------------------------------------------------------------- */
 /* Device status word of the current device: 0, or the code of the first bounded wait that expired (1-5, 8), of a
