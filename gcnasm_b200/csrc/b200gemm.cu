@@ -437,7 +437,11 @@ int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    // A launch that waits for ready words starts in plain stream order, after its predecessor has COMPLETED.  With
+    // programmatic serialization its first CTAs would be placed on whatever SMs the predecessor leaves free -- the very
+    // SMs a capped grid (B200GEMM_MAX_SMS) sets aside for the collective that delivers the slabs -- and spin there on
+    // words that collective can then never write.
+    cfg.numAttrs = p.batch_ready ? 0 : 1;
     CU_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
     g_launches.fetch_add(1);
     return B200_OK;

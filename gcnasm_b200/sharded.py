@@ -54,13 +54,23 @@ def slab_bytes(rows: int, k: int) -> int:
     return rows * k + 4 * (k // 128) * rows
 
 
-def configure_overlap(world: int, sm_count: int = 148, comm_sms: int = 4) -> None:
+def default_comm_sms(world: int) -> int:
+    """SMs to leave to NCCL beside the GEMM.  Measured on 8 x B200 (NVSwitch) with the 138 MB activation of the
+    16384 x 57344 x 8192 problem: a ring broadcast moves 18-26 GB/s per channel (one CTA each), so 4 channels deliver the
+    activation in 1.3 ms between 2 ranks but need 1.9 ms around 8, against GEMMs of 4.7 ms (2 ranks), 2.0 ms (4) and
+    1.0-1.15 ms (8); 6 channels need 1.4 ms at 8 ranks, 8 channels 1.1 ms but cost the GEMM another round of tiles."""
+    return 4 if world <= 2 else 6
+
+
+def configure_overlap(world: int, sm_count: int = 148, comm_sms: Optional[int] = None) -> None:
     """Call before the process group is created.  The GEMM kernels are persistent -- one CTA per SM until the last
     tile -- so a collective that is to run BESIDE a GEMM needs SMs the GEMM does not occupy: the GEMM grid is capped at
     ``sm_count - comm_sms`` SMs and NCCL is held to ``comm_sms`` channels (one CTA each, no CTA clusters, so that any
     free SM will do).  Existing settings of the variables win."""
     if world <= 1:
         return
+    if comm_sms is None:
+        comm_sms = default_comm_sms(world)
     os.environ.setdefault("NCCL_MAX_NCHANNELS", str(comm_sms))
     os.environ.setdefault("NCCL_MIN_NCHANNELS", str(comm_sms))
     os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "0")
@@ -217,7 +227,8 @@ class ColumnShardedGemm:
             self._ready = [torch.zeros(plan.slabs, dtype=torch.int32, device=device) for _ in range(nbuf)]
             self._gemm_done = [None] * nbuf
             self._posted = [None] * nbuf
-            self._comm = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+            # high priority: when an SM frees up, a pending block of the delivery goes before a pending block of a GEMM
+            self._comm = torch.cuda.Stream(device=device, priority=-1) if device.type == "cuda" else None
             # may a collective run BESIDE a GEMM that is waiting for it?  Only when the GEMM grid leaves SMs free
             # (configure_overlap); a single rank has no collective to starve
             self.overlap = True

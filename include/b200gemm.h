@@ -93,7 +93,9 @@ typedef struct b200_gemm_args {
  * the slab -- a copy or a collective on another stream, a peer GPU -- writes the word after the slab's last byte,
  * e.g. with b200_flag_write on the delivering stream.  B, SFB and C are not covered: B must be resident, and C is
  * ordered like any other launch.  Words only grow (use a step counter as epoch), so nothing is ever cleared.
- * Implies that A does not depend on the previous kernel of the stream (the ready words order it instead).
+ * Such a launch starts in plain stream order, after its predecessor has completed (no programmatic early start: its
+ * first CTAs would otherwise occupy the SMs a capped grid leaves to the collective that delivers the slabs, and
+ * wait there for words that collective could then never write).
  * Only the 2-CTA tile kernels implement it: M > 128 per batch and scale mode NONE, TENSOR or BLOCK, else
  * B200_ERR_UNSUPPORTED.
  * A batched problem may share one B: stride_b_batch == 0 (and stride_sfb_batch == 0) makes every batch multiply
