@@ -206,7 +206,7 @@ def workload_config(world):
     m, n, k = C5
     return {"workload": f"c5_blockscale_M{m}_N{n}_K{k}_sharded_over_{world}",
             "scales": "A 1x128 fp32 [K/128][M], B 128x128 fp32", "out": "bf16", "seed": SEED,
-            "parallelism": (f"B column-sharded x{world} ({n // world} columns per rank), A+SFA NCCL broadcast from rank 0 every call "
+            "parallelism": (f"B column-sharded x{world} ({n // world} columns per rank), A+SFA sent from rank 0 to every rank every call "
                             "in row slabs, outputs stay sharded" if world > 1 else "single GPU, whole problem"),
             "l2": "operands of one call (A+SFA 138 MB, B shard >= 59 MB, C shard >= 235 MB) exceed the 126 MB L2; two activation "
                   "and two output buffers alternate"}
@@ -223,6 +223,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--min-timed-s", type=float, default=0.5)
+    ap.add_argument("--delivery", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the activation slabs reach the ranks (copy-engine chain, or NCCL broadcasts)")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL beside the persistent GEMM grid (N > 1); 0 = the package's default")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -248,8 +250,11 @@ def main():
     dev = torch.device("cuda", local_rank)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     if world > 1:
-        args.comm_sms = args.comm_sms or default_comm_sms(world)
-        configure_overlap(world, sms, args.comm_sms)
+        if args.delivery == "nccl":
+            args.comm_sms = args.comm_sms or default_comm_sms(world)
+            configure_overlap(world, sms, args.comm_sms)
+        else:
+            args.comm_sms = 0                      # the copy engines deliver: the GEMM keeps every SM
         opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)     # NCCL's kernels before pending GEMM blocks
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
@@ -294,7 +299,7 @@ def main():
         qb[c0:c0 + chunk].copy_(q)
         sfb[c0 // 128:(c0 + chunk) // 128].copy_(s)
         del xb, q, s
-    op = ColumnShardedGemm(qb, sfb, n_total)
+    op = ColumnShardedGemm(qb, sfb, n_total, delivery=args.delivery)
     plan = op.plan_slabs(m, k, dev, nbuf=2)
     if rank == 0:
         # two activations (N(0,1), two seeded streams), quantised once straight into the two ring buffers; they
@@ -419,31 +424,59 @@ def main():
         torch.cuda.synchronize()
         kern.append(a0.elapsed_time(a1))
     idle_ms = allmax(float(np.mean(kern)))
-    # the delivery on its own: one call's slabs (root: already in the buffer) broadcast and flagged, no GEMM beside it
+    # One call on its own, delivery included: every rank idle, then post + run.  What it takes beyond the kernel is the
+    # part of the delivery that a single call cannot hide (the first slab's way down to the last rank).  With NCCL the
+    # whole delivery is also timed without any GEMM beside it.
+    def drain():
+        i = state["next"]
+        if state["posted"] >= i:                   # a step posted ahead by the loop: run it so that the ring stays in step
+            op.run(i, outs[i % 2])
+            state["next"] = i + 1
+
     delivery = None
     if world > 1:
-        dl = []
+        iso, dl = [], []
         for _ in range(4):
+            drain()
             i = state["next"]
             torch.cuda.synchronize()
             dist.barrier()
-            d0, d1 = ev(), ev()
-            with torch.cuda.stream(op._comm):
-                d0.record()
+            c0, c1 = ev(), ev()
+            c0.record()
             op.post(i, prefilled=True)
             state["posted"] = i
-            with torch.cuda.stream(op._comm):
-                d1.record()
+            op.run(i, outs[i % 2])
+            c1.record()
             torch.cuda.synchronize()
-            dl.append(d0.elapsed_time(d1))
-            op.run(i, outs[i % 2])                 # consume it, so that the step counter and the ring stay in step
             state["next"] = i + 1
+            iso.append(c0.elapsed_time(c1))
+        if op.delivery == "nccl":
+            for _ in range(4):
+                drain()
+                i = state["next"]
+                torch.cuda.synchronize()
+                dist.barrier()
+                d0, d1 = ev(), ev()
+                with torch.cuda.stream(op._comm):
+                    d0.record()
+                op.post(i, prefilled=True)
+                state["posted"] = i
+                with torch.cuda.stream(op._comm):
+                    d1.record()
+                torch.cuda.synchronize()
+                dl.append(d0.elapsed_time(d1))
+            drain()
         torch.cuda.synchronize()
         dbytes = plan.slabs * plan.bytes_per_slab
-        dms = allmax(float(np.median(dl)))
-        delivery = {"collective": f"ncclBroadcast x {plan.slabs} slabs of {plan.bytes_per_slab} bytes + {plan.slabs} ready-word writes",
-                    "ms_alone": dms, "bytes": dbytes, "gbs": dbytes / dms / 1e6,
-                    "nccl_channels": os.environ.get("NCCL_MAX_NCHANNELS"), "hidden_behind_gemm_ms": kern_ms}
+        iso_ms = allmax(float(np.median(iso)))
+        delivery = {"how": ("ncclBroadcast per slab on a side stream, NCCL held to %s channels" % os.environ.get("NCCL_MAX_NCHANNELS")
+                            if op.delivery == "nccl" else
+                            "copy-engine pushes down the chain of ranks (b200_stream_copy over peer-mapped memory), no SM"),
+                    "slabs": plan.slabs, "bytes": dbytes, "isolated_call_ms": iso_ms, "kernel_ms": kern_ms,
+                    "exposed_in_isolated_call_ms": iso_ms - kern_ms}
+        if dl:
+            dms = allmax(float(np.median(dl)))
+            delivery.update({"ms_alone": dms, "gbs_alone": dbytes / dms / 1e6})
     flop_local = 2.0 * m * n * k
     achieved = flop_local / (kern_ms * 1e-3) / 1e12
     traffic_8 = C5_SHARD_DRAM_BYTES
@@ -518,6 +551,7 @@ def main():
     # ---- sections at N=1 ---------------------------------------------------------------------------------------
     sections = {}
     want = ALL_SECTIONS if args.sections == "all" else tuple(s for s in args.sections.split(",") if s and s != "none")
+    op.close()
     del outs, op, qb, sfb
     torch.cuda.empty_cache()
     if world == 1:
@@ -538,6 +572,7 @@ def main():
             "run": {"calls_per_step": calls_per_step, "ms_per_call": ms_step / calls_per_step,
                     "slabs": f"{plan.slabs} x {plan.rows} rows, {plan.bytes_per_slab} bytes each, {plan.nbuf} activation buffers",
                     "launch": "one GEMM launch per call (slabs = batches, ready words), chained by programmatic dependent launch",
+                    "delivery": args.delivery if world > 1 else "none (single rank)",
                     "comm_sms": args.comm_sms if world > 1 else 0, "gemm_sms": int(L.lib().b200_sm_count())},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "parity_checked": parity["checked"], "parity": parity, "device_status": status, "inner_repeats": calls_per_step,

@@ -32,7 +32,8 @@ EXPORTS = (
     "b200_quantize_act_bf16_1x128", "b200_quantize_act_bf16_mx32", "b200_membw_read", "b200_membw_copy",
     "b200_weight_file_write", "b200_weight_file_stat", "b200_weight_file_read",
     "b200_fill_uniform", "b200_fill_normal",
-    "b200_flag_write", "b200_slab_bytes", "b200_slab_upload", "b200_last_status", "b200_peek_status", "b200_selftest_bounded_wait", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
+    "b200_flag_write", "b200_flag_wait", "b200_stream_copy", "b200_ipc_alloc", "b200_ipc_open", "b200_ipc_close", "b200_ipc_free",
+    "b200_slab_bytes", "b200_slab_upload", "b200_last_status", "b200_peek_status", "b200_selftest_bounded_wait", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
     "b200_version", "b200_launch_count",
 )
 
@@ -109,6 +110,12 @@ def lib() -> C.CDLL:
         "b200_fill_uniform": (None, [vp, sz, u64, u32, f32, f32]),
         "b200_fill_normal": (None, [vp, sz, u64, u32]),
         "b200_flag_write": (i32, [vp, i32, vp]),
+        "b200_flag_wait": (i32, [vp, i32, vp]),
+        "b200_stream_copy": (i32, [vp, vp, sz, vp]),
+        "b200_ipc_alloc": (i32, [sz, C.POINTER(vp), vp]),
+        "b200_ipc_open": (i32, [vp, C.POINTER(vp)]),
+        "b200_ipc_close": (i32, [vp]),
+        "b200_ipc_free": (i32, [vp]),
         "b200_slab_bytes": (sz, [i64, i64]),
         "b200_slab_upload": (i32, [vp, vp, vp, i64, i64, i64, i64, vp]),
         "b200_last_status": (i32, []),

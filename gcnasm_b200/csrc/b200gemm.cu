@@ -64,6 +64,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn g_encode = nullptr;
 typedef CUresult (*StreamWriteValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
 StreamWriteValue32Fn g_write_value32 = nullptr;     // null when the driver does not offer stream memory operations
+StreamWriteValue32Fn g_wait_value32 = nullptr;      // cuStreamWaitValue32 has the same signature
 
 
 int device_state(DeviceState** out) {
@@ -102,6 +103,12 @@ int device_state(DeviceState** out) {
             if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &wv, cudaEnableDefault, &q) == cudaSuccess &&
                 q == cudaDriverEntryPointSuccess && wv)
                 g_write_value32 = reinterpret_cast<StreamWriteValue32Fn>(wv);
+            else
+                cudaGetLastError();
+            wv = nullptr;
+            if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &wv, cudaEnableDefault, &q) == cudaSuccess &&
+                q == cudaDriverEntryPointSuccess && wv)
+                g_wait_value32 = reinterpret_cast<StreamWriteValue32Fn>(wv);
             else
                 cudaGetLastError();
         }
@@ -1233,6 +1240,64 @@ int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream) {
     // A driver without stream memory operations: a one-thread kernel could do the write, but it would need an SM,
     // and the consumer of these words is a persistent GEMM that may hold every SM while it waits for them.
     return B200_ERR_UNSUPPORTED;
+}
+int b200_flag_wait(const int32_t* flag, int32_t value, void* cuda_stream) {
+    if (!flag || (reinterpret_cast<uintptr_t>(flag) & 3)) return B200_ERR_BAD_ARG;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    if (!g_wait_value32) return B200_ERR_UNSUPPORTED;
+    const CUresult r = g_wait_value32(reinterpret_cast<CUstream>(cuda_stream), reinterpret_cast<CUdeviceptr>(flag),
+                                      static_cast<cuuint32_t>(value), 0x0 /* CU_STREAM_WAIT_VALUE_GEQ */);
+    if (r == CUDA_SUCCESS) return B200_OK;
+    g_last_cuda = 100000 + static_cast<int>(r);
+    return B200_ERR_CUDA;
+}
+int b200_stream_copy(void* dst, const void* src, size_t bytes, void* cuda_stream) {
+    if (!dst || !src || bytes == 0) return B200_ERR_BAD_ARG;
+    CU_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(cuda_stream)));
+    return B200_OK;
+}
+int b200_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    if (!dev_ptr || !handle64 || bytes == 0) return B200_ERR_BAD_ARG;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    void* p = nullptr;
+    CU_TRY(cudaMalloc(&p, bytes));
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        g_last_cuda = static_cast<int>(e);
+        cudaFree(p);
+        return B200_ERR_CUDA;
+    }
+    std::memcpy(handle64, &h, sizeof(h));
+    *dev_ptr = p;
+    return B200_OK;
+}
+int b200_ipc_open(const void* handle64, void** dev_ptr) {
+    if (!handle64 || !dev_ptr) return B200_ERR_BAD_ARG;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    CU_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *dev_ptr = p;
+    return B200_OK;
+}
+int b200_ipc_close(void* dev_ptr) {
+    if (!dev_ptr) return B200_ERR_BAD_ARG;
+    CU_TRY(cudaIpcCloseMemHandle(dev_ptr));
+    return B200_OK;
+}
+int b200_ipc_free(void* dev_ptr) {
+    if (!dev_ptr) return B200_ERR_BAD_ARG;
+    CU_TRY(cudaFree(dev_ptr));
+    return B200_OK;
 }
 size_t b200_slab_bytes(int64_t slab_rows, int64_t k) {
     if (slab_rows <= 0 || k <= 0 || k % 128 != 0 || slab_rows % 4 != 0) return 0;

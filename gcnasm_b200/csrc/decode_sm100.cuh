@@ -235,13 +235,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
             // promotion multiplies by, formed once here instead of once per thread and group)
             const float* sfa_g = p.sfa + b * p.sfa_batch;
             const float* sfb_g = p.sfb + b * p.sfb_batch + static_cast<long long>(ni) * p.sfb_stride;
-            // (eight independent element loads in flight per thread: one element per round trip made this loop
-            // cost 0.35 us per 128 x MT elements, 10 us of a 37 us launch at MT = 64)
+            // (U independent element loads in flight per thread: with one element per round trip this loop cost
+            // 0.35 us per 128 x MT elements, 10 us of a 37 us launch at MT = 64.  Eight in flight cover a config-4 panel
+            // in 1, 2 and 4 round trips at MT = 16, 32, 64; the wider token blocks therefore keep 16 and 28 in flight --
+            // the accumulators are not live yet, so the registers are there.)
+            constexpr int U = MT <= 16 ? 8 : (MT <= 32 ? 16 : 28);
             const int total = nkb * MT;
-            for (int base = et; base < total; base += 128 * 8) {
-                float va[8], vb[8];
+            for (int base = et; base < total; base += 128 * U) {
+                float va[U], vb[U];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < U; ++u) {
                     const int idx = base + u * 128;
                     va[u] = 0.0f;
                     vb[u] = 0.0f;
@@ -254,7 +257,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) decode_a8w8_sm100_kernel(cons
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < U; ++u) {
                     const int idx = base + u * 128;
                     if (idx < total) sf_smem[idx] = va[u] * vb[u];
                 }

@@ -93,7 +93,10 @@ class ColumnShardedGemm:
     def __init__(self, b_shard: torch.Tensor, sfb_shard: torch.Tensor, n_total: int, group=None,
                  gemm_fn: Optional[Callable] = None, out_dtype=torch.bfloat16, quant_fn: Optional[Callable] = None,
                  slab_gemm_fn: Optional[Callable] = None, flag_fn: Optional[Callable] = None,
-                 upload_fn: Optional[Callable] = None):
+                 upload_fn: Optional[Callable] = None, delivery: str = "nccl"):
+        if delivery not in ("nccl", "peer"):
+            raise ValueError("delivery is 'nccl' (slab broadcasts) or 'peer' (copy-engine pushes down a chain of GPUs)")
+        self.delivery = delivery
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -143,6 +146,10 @@ class ColumnShardedGemm:
         self._posted: List[Optional[object]] = []
         self._comm = None
         self.overlap = True
+        self._chain = None               # peer delivery: this rank's part of the chain (gcnasm_b200.peer.SlabChain)
+        self._region = None              # ... and its shared region: (pointer, mapped neighbours)
+        self._credit_stream = None
+        self._fwd_done: List[Optional[object]] = []
 
     def check_agreement(self, m: int, k: int) -> None:
         """Host-side guard before a collective: every rank must be about to run the same (M, K).  A rank that
@@ -213,31 +220,91 @@ class ColumnShardedGemm:
     # ------------------------------------------------------------------------------------------------------
     # slab pipeline
     # ------------------------------------------------------------------------------------------------------
-    def plan_slabs(self, m: int, k: int, device, slab_rows: Optional[int] = None, nbuf: int = 2) -> SlabPlan:
+    def plan_slabs(self, m: int, k: int, device, slab_rows: Optional[int] = None, nbuf: int = 2, root: int = 0) -> SlabPlan:
         """Allocates ``nbuf`` activation buffers in the slab layout and their ready words (one int32 per slab and
-        buffer, never cleared: a step's epoch is its number + 1, and words only grow)."""
+        buffer, never cleared: a step's epoch is its number + 1, and words only grow).  With peer delivery this is a
+        collective call: the buffers live in a region the neighbours of the chain (which starts at ``root``) map."""
         rows = slab_rows or pick_slab_rows(m)
         if m % rows != 0:
             raise ValueError(f"M={m} is not a whole number of {rows}-row slabs")
         plan = SlabPlan(m, k, rows, m // rows, slab_bytes(rows, k), nbuf)
         device = torch.device(device)
         if self._plan != plan or not self._bufs or self._bufs[0].device != device:
+            self.close()
             self._plan = plan
-            self._bufs = [torch.empty(plan.slabs * plan.bytes_per_slab, dtype=torch.uint8, device=device) for _ in range(nbuf)]
-            self._ready = [torch.zeros(plan.slabs, dtype=torch.int32, device=device) for _ in range(nbuf)]
+            peer = self.delivery == "peer" and device.type == "cuda" and self.world > 1
+            if peer:
+                self._plan_peer_region(plan, device, root)
+            else:
+                self._bufs = [torch.empty(plan.slabs * plan.bytes_per_slab, dtype=torch.uint8, device=device) for _ in range(nbuf)]
+                self._ready = [torch.zeros(plan.slabs, dtype=torch.int32, device=device) for _ in range(nbuf)]
             self._gemm_done = [None] * nbuf
             self._posted = [None] * nbuf
+            self._fwd_done = [None] * nbuf
             # high priority: when an SM frees up, a pending block of the delivery goes before a pending block of a GEMM
             self._comm = torch.cuda.Stream(device=device, priority=-1) if device.type == "cuda" else None
+            self._credit_stream = torch.cuda.Stream(device=device, priority=-1) if peer else None
             # may a collective run BESIDE a GEMM that is waiting for it?  Only when the GEMM grid leaves SMs free
-            # (configure_overlap); a single rank has no collective to starve
+            # (configure_overlap); a single rank has no collective to starve, and peer delivery runs on the copy engines
             self.overlap = True
-            if device.type == "cuda" and self.world > 1:
+            if device.type == "cuda" and self.world > 1 and not peer:
                 from . import _lib as L
 
                 with torch.cuda.device(device):
                     self.overlap = L.lib().b200_sm_count() < torch.cuda.get_device_properties(device).multi_processor_count
         return plan
+
+    def _plan_peer_region(self, plan: SlabPlan, device, root: int) -> None:
+        import ctypes as C
+
+        from . import _lib as L
+        from .peer import CudaPeerOps, RegionLayout, SlabChain, chain_neighbours
+
+        lay = RegionLayout(plan.slabs, plan.bytes_per_slab, plan.nbuf)
+        with torch.cuda.device(device):
+            ptr, handle = C.c_void_p(), (C.c_ubyte * 64)()
+            L.check(L.lib().b200_ipc_alloc(lay.total_bytes, C.byref(ptr), handle), "b200_ipc_alloc")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=self.group)
+            down_rank, up_rank = chain_neighbours(self.rank, self.world, root)
+            mapped = {}
+            for r in {down_rank, up_rank} - {None}:
+                p = C.c_void_p()
+                L.check(L.lib().b200_ipc_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(p)), "b200_ipc_open")
+                mapped[r] = p.value
+
+        class _Raw:                                                 # a torch tensor over the region, without a copy
+            __cuda_array_interface__ = {"shape": (lay.total_bytes,), "typestr": "|u1", "data": (ptr.value, False), "version": 2}
+
+        whole = torch.as_tensor(_Raw(), device=device)
+        whole.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)                              # nobody pushes into a region that is still being cleared
+        per = plan.slabs * plan.bytes_per_slab
+        self._bufs = [whole[i * per:(i + 1) * per] for i in range(plan.nbuf)]
+        words = whole[lay.ready_off:lay.ready_off + 4 * plan.nbuf * plan.slabs].view(torch.int32)
+        self._ready = [words[i * plan.slabs:(i + 1) * plan.slabs] for i in range(plan.nbuf)]
+        self._region = (ptr.value, mapped, whole)
+        self._chain = SlabChain(lay, CudaPeerOps(), ptr.value, mapped.get(down_rank), mapped.get(up_rank), self.rank == root)
+        self._chain_root = root
+
+    def close(self) -> None:
+        """Releases the peer-mapped region (a collective call when peer delivery is in use; a no-op otherwise)."""
+        if self._region is None:
+            return
+        from . import _lib as L
+
+        ptr, mapped, whole = self._region
+        torch.cuda.synchronize(whole.device)
+        dist.barrier(group=self.group)                              # every rank has stopped pushing
+        self._bufs, self._ready, self._chain, self._region = [], [], None, None
+        del whole
+        with torch.cuda.device(self._comm.device):
+            for p in mapped.values():
+                L.lib().b200_ipc_close(p)
+            dist.barrier(group=self.group)                          # ... and unmapped, before the owner frees
+            L.lib().b200_ipc_free(ptr)
+        self._plan = None
 
     def slab_views(self, buf_index: int):
         """(bytes [slabs, bytes_per_slab], A [slabs, rows, K], SFA [slabs, K/128, rows]) over activation buffer ``buf_index``."""
@@ -245,8 +312,9 @@ class ColumnShardedGemm:
         buf = self._bufs[buf_index]
         kg = p.k // 128
         a3 = torch.as_strided(buf, (p.slabs, p.rows, p.k), (p.bytes_per_slab, p.k, 1))
-        sfa3 = torch.as_strided(buf.view(torch.float32), (p.slabs, kg, p.rows), (p.bytes_per_slab // 4, p.rows, 1),
-                                storage_offset=p.rows * p.k // 4)
+        fbuf = buf.view(torch.float32)                     # (a buffer may itself be a slice of a larger region)
+        sfa3 = torch.as_strided(fbuf, (p.slabs, kg, p.rows), (p.bytes_per_slab // 4, p.rows, 1),
+                                storage_offset=fbuf.storage_offset() + p.rows * p.k // 4)
         return buf.view(p.slabs, p.bytes_per_slab), a3, sfa3
 
     def _on_comm(self):
@@ -296,6 +364,21 @@ class ColumnShardedGemm:
                 if on_gpu:
                     filled[s] = torch.cuda.Event()
                     filled[s].record()
+        if self._chain is not None:
+            if root != self._chain_root:
+                raise ValueError("peer delivery was planned for another root")
+
+            def before_slab(s):
+                if from_host:
+                    self.upload_fn(a, sfa, self._bufs[buf_index], p.m, p.k, p.rows, s)
+                elif filled[s] is not None:
+                    self._comm.wait_event(filled[s])
+
+            with self._on_comm():
+                self._chain.forward(step, before_slab if is_root else None)
+                self._fwd_done[buf_index] = torch.cuda.Event()
+                self._fwd_done[buf_index].record()
+            return
         with self._on_comm():
             for s in range(p.slabs):
                 if from_host:
@@ -327,6 +410,13 @@ class ColumnShardedGemm:
             ev = torch.cuda.Event()
             ev.record()
             self._gemm_done[buf_index] = ev
+        if self._chain is not None:
+            # this rank is done with the buffer once its GEMM has read it and its forwarding has copied it on
+            with torch.cuda.stream(self._credit_stream):
+                self._credit_stream.wait_event(self._gemm_done[buf_index])
+                if self._fwd_done[buf_index] is not None:
+                    self._credit_stream.wait_event(self._fwd_done[buf_index])
+                self._chain.credit(step)
         return out
 
     def step(self, step: int, out: torch.Tensor, **source) -> torch.Tensor:

@@ -247,6 +247,27 @@ void b200_fill_normal(float* host_out, size_t count, uint64_t seed, uint32_t ten
  * No counterpart in the reference (its kernels never wait for data).                                             */
 int b200_flag_write(int32_t* flag, int32_t value, void* cuda_stream);
 
+/* ---- peer memory: slabs pushed from GPU to GPU by the copy engines ------------------------------------------- */
+/* For the N-sharded mode with one process per GPU.  The activation of a call can travel down a chain of GPUs without
+ * any kernel: every rank copies a slab it has received into the next rank's buffer with a device-to-device copy (copy
+ * engines over NVLink), then writes that rank's ready word; the consumer is the GEMM of B200_GEMM_BATCH_READY.  These
+ * entry points are the pieces: memory another process can map, the mapping, a stream-ordered copy, and a stream-
+ * ordered wait on a word.  The reference has no counterpart (one GPU, one process).
+ * b200_ipc_alloc: cudaMalloc on the current device plus the 64-byte handle (cudaIpcMemHandle_t) another process on
+ * the same machine passes to b200_ipc_open, which maps the memory into the caller and enables peer access between
+ * the two devices.  b200_ipc_close unmaps, b200_ipc_free frees (only the allocating process, after every peer has
+ * closed).  How the handle reaches the peer is the caller's business.                                             */
+int b200_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64);
+int b200_ipc_open(const void* handle64, void** dev_ptr);
+int b200_ipc_close(void* dev_ptr);
+int b200_ipc_free(void* dev_ptr);
+/* Copy between device buffers (this GPU's or a mapped peer's) in stream order; no kernel is launched. */
+int b200_stream_copy(void* dst, const void* src, size_t bytes, void* cuda_stream);
+/* Everything queued on `cuda_stream` after this call waits until the device word `flag` (this GPU's memory) holds a
+ * value >= `value` (a stream memory operation: no kernel, no SM, no host thread).  The counterpart of b200_flag_write
+ * for words that ANOTHER GPU writes.  Nothing bounds this wait: only wait for words whose writer is already queued.  */
+int b200_flag_wait(const int32_t* flag, int32_t value, void* cuda_stream);
+
 /* ---- activation slabs ---------------------------------------------------------------------------------- */
 /* The layout in which the N-sharded mode moves a block-scale activation between GPUs and feeds it to a batched GEMM
  * (B200_GEMM_BATCH_READY): the M rows are cut into slabs of `slab_rows`, and slab s is ONE contiguous piece
