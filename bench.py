@@ -301,6 +301,7 @@ def main():
         del xb, q, s
     op = ColumnShardedGemm(qb, sfb, n_total, delivery=args.delivery)
     plan = op.plan_slabs(m, k, dev, nbuf=2)
+    delivery_used, delivery_note = op.delivery, op.delivery_note       # "nccl" with a note if the GPUs cannot map each other
     if rank == 0:
         # two activations (N(0,1), two seeded streams), quantised once straight into the two ring buffers; they
         # stay resident in HBM, and every step broadcasts one of them again
@@ -572,7 +573,7 @@ def main():
             "run": {"calls_per_step": calls_per_step, "ms_per_call": ms_step / calls_per_step,
                     "slabs": f"{plan.slabs} x {plan.rows} rows, {plan.bytes_per_slab} bytes each, {plan.nbuf} activation buffers",
                     "launch": "one GEMM launch per call (slabs = batches, ready words), chained by programmatic dependent launch",
-                    "delivery": args.delivery if world > 1 else "none (single rank)",
+                    "delivery": (delivery_used + (": " + delivery_note if delivery_note else "")) if world > 1 else "none (single rank)",
                     "comm_sms": args.comm_sms if world > 1 else 0, "gemm_sms": int(L.lib().b200_sm_count())},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "parity_checked": parity["checked"], "parity": parity, "device_status": status, "inner_repeats": calls_per_step,

@@ -77,6 +77,10 @@ def configure_overlap(world: int, sm_count: int = 148, comm_sms: Optional[int] =
     os.environ.setdefault("B200GEMM_MAX_SMS", str(sm_count - comm_sms))
 
 
+class PeerDeliveryUnavailable(RuntimeError):
+    """The GPUs of this job cannot map each other's memory (every rank raises it together)."""
+
+
 @dataclass
 class SlabPlan:
     m: int
@@ -97,6 +101,7 @@ class ColumnShardedGemm:
         if delivery not in ("nccl", "peer"):
             raise ValueError("delivery is 'nccl' (slab broadcasts) or 'peer' (copy-engine pushes down a chain of GPUs)")
         self.delivery = delivery
+        self.delivery_note = ""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -234,8 +239,12 @@ class ColumnShardedGemm:
             self._plan = plan
             peer = self.delivery == "peer" and device.type == "cuda" and self.world > 1
             if peer:
-                self._plan_peer_region(plan, device, root)
-            else:
+                try:
+                    self._plan_peer_region(plan, device, root)
+                except PeerDeliveryUnavailable as e:
+                    # said out loud, not hidden: the slabs then travel by NCCL broadcasts (delivery_note tells the caller)
+                    self.delivery, self.delivery_note, peer = "nccl", f"peer delivery unavailable ({e}); NCCL broadcasts instead", False
+            if not peer:
                 self._bufs = [torch.empty(plan.slabs * plan.bytes_per_slab, dtype=torch.uint8, device=device) for _ in range(nbuf)]
                 self._ready = [torch.zeros(plan.slabs, dtype=torch.int32, device=device) for _ in range(nbuf)]
             self._gemm_done = [None] * nbuf
@@ -261,17 +270,36 @@ class ColumnShardedGemm:
         from .peer import CudaPeerOps, RegionLayout, SlabChain, chain_neighbours
 
         lay = RegionLayout(plan.slabs, plan.bytes_per_slab, plan.nbuf)
+        down_rank, up_rank = chain_neighbours(self.rank, self.world, root)
+        mapped = {}
+        ptr, handle, why = C.c_void_p(), (C.c_ubyte * 64)(), ""
         with torch.cuda.device(device):
-            ptr, handle = C.c_void_p(), (C.c_ubyte * 64)()
-            L.check(L.lib().b200_ipc_alloc(lay.total_bytes, C.byref(ptr), handle), "b200_ipc_alloc")
+            # every rank goes through the same collectives whatever fails locally, then all agree on the outcome
+            try:
+                L.check(L.lib().b200_ipc_alloc(lay.total_bytes, C.byref(ptr), handle), "b200_ipc_alloc")
+            except Exception as e:                                  # noqa: BLE001 (reported, and every rank falls back)
+                why, ptr = str(e), C.c_void_p()
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=self.group)
-            down_rank, up_rank = chain_neighbours(self.rank, self.world, root)
-            mapped = {}
-            for r in {down_rank, up_rank} - {None}:
-                p = C.c_void_p()
-                L.check(L.lib().b200_ipc_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(p)), "b200_ipc_open")
-                mapped[r] = p.value
+            dist.all_gather_object(handles, bytes(handle) if ptr.value else None, group=self.group)
+            if not why and any(h is None for h in handles):
+                why = "another rank could not allocate its region"
+            if not why:
+                try:
+                    for r in {down_rank, up_rank} - {None}:
+                        p = C.c_void_p()
+                        L.check(L.lib().b200_ipc_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(p)), "b200_ipc_open")
+                        mapped[r] = p.value
+                except Exception as e:                              # noqa: BLE001
+                    why = str(e)
+            reasons = [None] * self.world
+            dist.all_gather_object(reasons, why, group=self.group)
+            if any(reasons):
+                for p in mapped.values():
+                    L.lib().b200_ipc_close(p)
+                dist.barrier(group=self.group)
+                if ptr.value:
+                    L.lib().b200_ipc_free(ptr)
+                raise PeerDeliveryUnavailable("; ".join(f"rank {i}: {w}" for i, w in enumerate(reasons) if w))
 
         class _Raw:                                                 # a torch tensor over the region, without a copy
             __cuda_array_interface__ = {"shape": (lay.total_bytes,), "typestr": "|u1", "data": (ptr.value, False), "version": 2}
