@@ -74,6 +74,7 @@ struct PairCfg {
 // UMMA issuer threads in block-scale mode (warps 1..kBlockIssuers of the leader CTA); at most the number of
 // TMEM buffers, because an issuer has to observe every phase of the barriers it waits on.
 static constexpr int kBlockIssuers = 2;
+
 // Building with -DB200_TRACE records clock64() stamps of the hand-offs of the first CTA pair into g_trace
 // (read back with b200_trace_read); it is how the latencies quoted in the comments here were measured.
 #ifdef B200_TRACE
@@ -305,12 +306,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && ((p.ldc * esz) % 16 == 0) &&
                             ((p.c_batch * esz) % 16 == 0);
         const uint32_t leader_acce0 = mapa_shared(bar_acce0, 0);
-        uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 +
-                             (Cfg::TILE_TMA ? ew * (32 * NCH * 2) : ew * kOutStageBytesPerWarp);
-        // this warp's part of the tile staging area: NCH/64 boxes of 32 rows x 128 bytes (1024-byte aligned)
-        const uint32_t tile_stage = smem_base + STAGES * Cfg::STAGE_BYTES + 1024 +
-                                    Cfg::OUT_STAGE_BYTES + ew * (32 * NCH * 2);
-        uint8_t* tile_stage_gen = smem_gen + (tile_stage - smem_base);
         bool stores_pending = false;
         bool c_ordered = !p.inputs_ready;           // writes to C must follow the previous kernel (see pdl_wait above)
         float tscale = 1.0f;
@@ -337,9 +332,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 }
             }
             const int row = mi * (2 * BM) + row_in_tile;
-            const int row0 = row - lane;                       // output row of this warp's lane 0
-            const int col_base = ni * BN + half * NCH;
-            uint8_t* cbatch = reinterpret_cast<uint8_t*>(p.c) + static_cast<size_t>(b) * p.c_batch * esz;
 
             if constexpr (MODE == MODE_BLOCK) {
                 unsigned long long acc[NCH / 2];
@@ -348,18 +340,27 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 // this thread's NCH columns touch at most two 128-wide scale blocks of B
                 // (with BN = 256 every thread's 128 columns are exactly one block: no second scale)
                 constexpr bool kStraddle = (BN % 256) != 0;
-                const int blk0 = col_base >> 7;
-                const int split = kStraddle ? ((blk0 + 1) << 7) - col_base : NCH;   // columns before the block boundary
+                const int col_first = ni * BN + half * NCH;
+                const int blk0 = col_first >> 7;
+                const int split = kStraddle ? ((blk0 + 1) << 7) - col_first : NCH;   // columns before the block boundary
                 const bool has1 = kStraddle && split < NCH && ((blk0 + 1) << 7) < p.n;
-                const bool col_ok = col_base < p.n;
+                const bool col_ok = col_first < p.n;
                 const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
                 const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(blk0) * p.sfb_stride;
+                const uint32_t taddr0 = tmem_base + tmem_lane + half * NCH;       // this thread's lane and first column
                 float sa_cur = __ldg(sfa_p);
                 float sb0_cur = col_ok ? __ldg(sfb_p) : 0.0f;
                 float sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
+                // 32-column loads into two register buffers, both in flight at the start; a 16-column tail when
+                // NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load has landed,
+                // before the last FMAs; the next group's scales are fetched after that arrive (an arrive waits for
+                // the thread's outstanding loads).
+                constexpr int LW = Cfg::LW;
+                constexpr int CFULL = NCH / LW, TAIL = NCH % LW;
+                constexpr int NLD = CFULL + (TAIL ? 1 : 0);          // loads per group
+                static_assert(TAIL == 0 || (LW == 32 && TAIL == 16), "tail load is 16 columns");
+                constexpr int REL = (NLD - 1) & ~1;                  // the wait at this chunk covers the final load
                 for (int g = 0; g < groups; ++g, ++phase) {
-                    const float s0 = sa_cur * sb0_cur, s1 = kStraddle ? sa_cur * sb1_cur : s0;
-                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
                     const uint32_t as = phase & 1;
                     const uint32_t aph = (phase >> 1) & 1;
                     if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
@@ -368,22 +369,19 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     B200_TRACE_EPI(6);
                     tc_fence_after();
-                    const uint32_t taddr = tmem_base + tmem_lane + as * BN + half * NCH;
+                    const uint32_t taddr = taddr0 + as * BN;
                     B200_TRACE_EPI(0);
-                    // 32-column loads into two register buffers, both in flight at the start; a 16-column tail
-                    // when NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load
-                    // has landed, before the last FMAs; the next group's scales are fetched after that arrive
-                    // (an arrive waits for the thread's outstanding loads).
-                    constexpr int LW = Cfg::LW;
-                    constexpr int CFULL = NCH / LW, TAIL = NCH % LW;
-                    constexpr int NLD = CFULL + (TAIL ? 1 : 0);          // loads per group
-                    static_assert(TAIL == 0 || (LW == 32 && TAIL == 16), "tail load is 16 columns");
                     float v[2][LW];
-                    tmem_ld<LW>(taddr, v[0]);
-                    if (NLD > 1) {
-                        if (CFULL > 1) tmem_ld<LW>(taddr + LW, v[1]);
-                        else tmem_ld16(taddr + LW, v[1]);
-                    }
+                    auto load_chunk = [&](const int c) {
+                        if (c < CFULL) tmem_ld<LW>(taddr + c * LW, v[c & 1]);
+                        else tmem_ld16(taddr + c * LW, v[c & 1]);
+                    };
+                    load_chunk(0);
+                    if (NLD > 1) load_chunk(1);
+                    // (only now: the scales were requested during the previous group and may still be on their way; the
+                    // multiply that waits for them must not stand between the barrier and the tensor-memory loads)
+                    const float s0 = sa_cur * sb0_cur, s1 = kStraddle ? sa_cur * sb1_cur : s0;
+                    const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
                     // tcgen05.wait::ld waits for every load in flight, so it is executed only before the even
                     // chunks: an odd chunk landed with its predecessor, and a wait there would stall on the
                     // refill load issued a moment earlier
@@ -401,11 +399,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             }
                         }
                     };
-                    auto load_chunk = [&](const int c) {
-                        if (c < CFULL) tmem_ld<LW>(taddr + c * LW, v[c & 1]);
-                        else tmem_ld16(taddr + c * LW, v[c & 1]);
-                    };
-                    constexpr int REL = (NLD - 1) & ~1;                  // the wait at this chunk covers the final load
 #pragma unroll
                     for (int c = 0; c < NLD; ++c) {
                         if ((c & 1) == 0) {
@@ -432,10 +425,31 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                     B200_TRACE_EPI(2);
                 }
+                if (!ok) break;
                 if (!c_ordered) {
                     pdl_wait();
                     c_ordered = true;
                 }
+                // Everything the store phase needs is derived again from the tile index here, behind an opaque copy of
+                // it: nothing of it then has to stay in a register across the K loop, where the accumulators and the two
+                // load buffers leave none to spare.
+                int t_s = t, ew_s = ew;
+                uint32_t sb_s = smem_base;
+                asm volatile("" : "+r"(t_s), "+r"(ew_s), "+r"(sb_s));
+                uint8_t* smem_gen_s = smem_raw + (sb_s - smem_u32(smem_raw));
+                int b_s, mi_s, ni_s;
+                tile_coords(p, t_s, b_s, mi_s, ni_s);
+                const int half_s = ew_s >> 2;
+                const int row0 = mi_s * (2 * BM) + static_cast<int>(cta) * BM + (ew_s & 3) * 32;   // output row of lane 0
+                const int col_base = ni_s * BN + half_s * NCH;
+                const int b = b_s;
+                uint8_t* cbatch = reinterpret_cast<uint8_t*>(p.c) + static_cast<size_t>(b_s) * p.c_batch * esz;
+                uint8_t* out_stage = smem_gen_s + STAGES * Cfg::STAGE_BYTES + 1024 +
+                                     (Cfg::TILE_TMA ? ew_s * (32 * NCH * 2) : ew_s * kOutStageBytesPerWarp);
+                // this warp's part of the tile staging area: NCH/64 boxes of 32 rows x 128 bytes (1024-byte aligned)
+                const uint32_t tile_stage = sb_s + STAGES * Cfg::STAGE_BYTES + 1024 +
+                                            Cfg::OUT_STAGE_BYTES + ew_s * (32 * NCH * 2);
+                uint8_t* tile_stage_gen = smem_gen_s + (tile_stage - sb_s);
                 if (ok && Cfg::TILE_TMA && p.c_tma) {
                     // bf16 tile -> shared memory in the 128-byte-swizzled layout of the TMA box (16-byte piece c of
                     // row r sits at piece c ^ (r & 7): conflict-free for the row-per-lane register layout), then
@@ -499,6 +513,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     }
                 }
             } else {
+                const int row0 = row - lane;                       // output row of this warp's lane 0
+                const int col_base = ni * BN + half * NCH;
+                uint8_t* cbatch = reinterpret_cast<uint8_t*>(p.c) + static_cast<size_t>(b) * p.c_batch * esz;
+                uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 + ew * kOutStageBytesPerWarp;
                 const uint32_t as = phase % ACC_STAGES;
                 const uint32_t aph = (phase / ACC_STAGES) & 1;
                 if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
