@@ -43,8 +43,9 @@ import numpy as np  # noqa: E402
 
 C5 = (16384, 57344, 8192)          # M, N (whole problem), K
 SEED = 1234
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the block-scale pair kernel on 16384 x 7168 x 8192 (ncu)
-C5_SHARD_DRAM_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from ncu captures of exactly these
+# launches (columns per launch -> bytes): the whole problem on one GPU, and the per-rank launch of 8 ranks
+C5_DRAM_BYTES = {57344: 10.37e9, 7168: 824.9e6}
 ALL_SECTIONS = ("c2", "cube8192_blockscale", "cube8192_mx", "c1_per_tensor", "decode", "act_quant", "hbm_probe", "a16w16")
 
 
@@ -480,12 +481,12 @@ def main():
             delivery.update({"ms_alone": dms, "gbs_alone": dbytes / dms / 1e6})
     flop_local = 2.0 * m * n * k
     achieved = flop_local / (kern_ms * 1e-3) / 1e12
-    traffic_8 = C5_SHARD_DRAM_BYTES
+    traffic = C5_DRAM_BYTES.get(n)
     roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                "traffic": (traffic_8 * (n / 7168.0)) if traffic_8 else None,
-                "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at 16384x7168x8192 (the "
-                                   "shape one of 8 ranks runs), scaled by this launch's columns / 7168"
-                                   if traffic_8 else "no ncu capture of this shape has been taken"),
+                "traffic": traffic,
+                "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of exactly this shape "
+                                   "(profiles/gemm_pair_blockscale_c5_16384x57344x8192.md)" if traffic else
+                                   "no ncu capture of this rank count's launch (captured: 1 and 8 ranks; B re-reads do not scale with N)"),
                 "kernel": "gemm_a8w8_pair_sm100_kernel<PairCfg<256, block-scale, row-major B>>",
                 "kernel_ms": kern_ms, "launches_timed": reps, "timing": "launches of this kernel alone, back to back in stream order",
                 "kernel_ms_idle_device": idle_ms,
