@@ -484,8 +484,8 @@ def main():
     traffic = C5_DRAM_BYTES.get(n)
     roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                 "traffic": traffic,
-                "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of exactly this shape "
-                                   "(profiles/gemm_pair_blockscale_c5_16384x57344x8192.md)" if traffic else
+                "traffic_source": ("ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum -k regex:gemm_a8w8_pair, one launch of "
+                                   "exactly this shape, captured separately (a constant in this script, not measured in this run)" if traffic else
                                    "no ncu capture of this rank count's launch (captured: 1 and 8 ranks; B re-reads do not scale with N)"),
                 "kernel": "gemm_a8w8_pair_sm100_kernel<PairCfg<256, block-scale, row-major B>>",
                 "kernel_ms": kern_ms, "launches_timed": reps, "timing": "launches of this kernel alone, back to back in stream order",

@@ -53,6 +53,7 @@ struct Options {
     std::string save_weights = "", load_weights = "";  // flatmm: weight file written after / read instead of the shuffle
     std::string dist = "ref";                      // ref: A~U[0,1) B~U[-.5,.5) as the reference; u11: U[-1,1]; n01: N(0,1)
     int tile = 0;
+    int gpus = 1;                                  // blockscale: B sharded along N over this many GPUs of the machine
     bool json = false;
 };
 
@@ -90,6 +91,7 @@ inline Options parse(int argc, char** argv, int default_verify) {
         else if (take(argc, argv, i, nullptr, "--out", v)) o.out = v;
         else if (take(argc, argv, i, nullptr, "--dist", v)) o.dist = v;
         else if (take(argc, argv, i, nullptr, "--tile", v)) o.tile = std::atoi(v.c_str());
+        else if (take(argc, argv, i, nullptr, "--gpus", v)) o.gpus = std::atoi(v.c_str());
         else if (take(argc, argv, i, nullptr, "--warmup", v)) o.warmup = std::atoi(v.c_str());
         else if (take(argc, argv, i, nullptr, "--iters", v)) o.iters = std::atoi(v.c_str());
         else if (take(argc, argv, i, nullptr, "--save-weights", v)) o.save_weights = v;

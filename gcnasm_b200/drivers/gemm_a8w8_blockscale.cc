@@ -3,11 +3,13 @@
 // opus_gemm/block_scale_gemm/gemm_a8w8_blockscale_host.cc:128-294 (flags -m -n -k -b -v in both
 // "-m 4096" and "-m=4096" forms, verification off unless -v 1, absolute threshold 1e-3, the same
 // printed lines); the launch at :257 is replaced by b200_gemm_a8w8().
-// Additions: --dist n01|u11 quantises seeded source data with group amax/448 on the device;
+// Additions: --gpus R shards B along N over R GPUs of the machine (sharded_blockscale.h; activation uploaded on GPU 0 and
+// pushed from GPU to GPU every call); --dist n01|u11 quantises seeded source data with group amax/448 on the device;
 // --scale mx runs the MXFP8 1x32 E8M0 variant; --out bf16; --seed; --json; --act-bf16 (with --dist) hands the
 // activations over in bf16 and quantises them with the fused one-pass kernel (b200_quantize_act_bf16_1x128 /
 // _mx32) instead of the fp32 quantiser + re-layout.
 #include "driver_common.h"
+#include "sharded_blockscale.h"
 
 using namespace drv;
 
@@ -66,6 +68,13 @@ int main(int argc, char** argv) {
     if (mx && o.batch != 1) {
         std::fprintf(stderr, "MX driver runs batch 1.\n");
         return 1;
+    }
+    if (o.gpus > 1) {
+        if (mx) {
+            std::fprintf(stderr, "--gpus runs the fp32 block-scale variant.\n");
+            return 1;
+        }
+        return run_sharded(o, o.gpus);
     }
     const bool bf16 = o.out == "bf16";
     const bool quantise = mx || o.dist != "ref";

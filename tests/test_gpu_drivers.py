@@ -106,3 +106,20 @@ def test_blockscale_driver_overlap_flag(drivers):
     out = run(drivers, "gemm_a8w8_blockscale", "-m", "1024", "-n", "1792", "-k", "1024", "-b", "1", "-v", "1", "--overlap")
     assert "FAIL" not in out and "VALID" in out
     assert re.search(r"Kernel Performance: avg_time=\d+\.\d+ ms, \d+\.\d+ TFlops", out)
+
+
+def test_blockscale_driver_sharded_over_gpus(drivers):
+    """--gpus R: one host process, B sharded along N, the activation pushed from GPU to GPU by the copy engines and
+    consumed slab by slab through ready words; every shard is checked on its own GPU."""
+    import torch
+
+    gpus = min(torch.cuda.device_count(), 4)
+    if gpus < 2:
+        pytest.skip("needs at least two GPUs")
+    out = run(drivers, "gemm_a8w8_blockscale", "--gpus", str(gpus), "-m", "1024", "-n", str(512 * gpus), "-k", "1024", "-b", "1",
+              "-v", "1", "--out", "bf16", "--json")
+    assert f"gpus={gpus}" in out and "ALL SHARDS VALID" in out and "FAIL" not in out
+    assert out.count("VALID") == gpus + 1
+    assert '"status": 0' in out
+    bad = subprocess.run([os.path.join(drivers, "gemm_a8w8_blockscale"), "--gpus", "64", "-b", "1"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "CUDA device" in bad.stderr
