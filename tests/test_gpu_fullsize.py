@@ -147,3 +147,36 @@ def test_a16w16_large_sampled_rows(api, O):
     assert torch.equal(c, api.gemm_a16w16(a, b, out_dtype=torch.float32))
     shard = api.gemm_a16w16(a, b[1024:2048], out_dtype=torch.float32)
     assert torch.equal(shard, c[:, 1024:2048])
+
+
+def test_config5_per_rank_gemm_full(api, O):
+    """BASELINE config 5 as one of 8 ranks runs it: M=16384, K=8192, a 7168-column weight shard, through the slab
+    pipeline of the sharded operator (8 slabs of 2048 rows as batches of one launch, one B, ready words).  Sampled rows on
+    the CPU oracle, two row blocks on the device checker, and the whole result bit-identical to the plain (unbatched)
+    launch of the same problem and from run to run."""
+    from gcnasm_b200.sharded import ColumnShardedGemm
+
+    m, n, k = 16384, 7168, 8192
+    qb, sfb = api.quantize_128x128(torch.from_numpy(api.fill_normal((n, k), 1234, 16)).to(DEV))
+    qa, sfa = api.quantize_1x128(torch.from_numpy(api.fill_normal((m, k), 1234, 0)).to(DEV))
+    op = ColumnShardedGemm(qb, sfb, n)
+    plan = op.plan_slabs(m, k, DEV)
+    assert (plan.slabs, plan.rows) == (8, 2048)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    op.step(0, out, a=qa, sfa=sfa)
+    status_ok(api)
+    hb, hsb = qb.cpu().numpy(), sfb.cpu().numpy()
+    for r in _rows(m, 4, 9):
+        ha = qa[r:r + 1].cpu().numpy()
+        hsa = sfa[:, r:r + 1].contiguous().cpu().numpy()
+        ref = O.bf16_bits_to_f32(O.gemm_ref_blockscale(ha, hb, hsa, hsb, out_bf16=True))
+        assert_close(O, out[r:r + 1].float().cpu().numpy(), ref, f"row {r}")
+    for row0 in (1920, 14336 + 512):
+        err, ref = op.check_rows(0, out, row0, 128)
+        assert err <= 1e-2 * ref, (row0, err, ref)
+    plain = api.gemm_a8w8_blockscale(qa, qb, sfa, sfb, out_dtype=torch.bfloat16)
+    assert torch.equal(plain, out)                       # the same tiles, the same order of additions
+    out2 = torch.zeros_like(out)
+    op.step(1, out2, a=qa, sfa=sfa)
+    status_ok(api)
+    assert torch.equal(out2, out)
