@@ -155,6 +155,7 @@ class ColumnShardedGemm:
         self._region = None              # ... and its shared region: (pointer, mapped neighbours)
         self._credit_stream = None
         self._fwd_done: List[Optional[object]] = []
+        self._next_step = 0
 
     def check_agreement(self, m: int, k: int) -> None:
         """Host-side guard before a collective: every rank must be about to run the same (M, K).  A rank that
@@ -237,6 +238,7 @@ class ColumnShardedGemm:
         if self._plan != plan or not self._bufs or self._bufs[0].device != device:
             self.close()
             self._plan = plan
+            self._next_step = 0
             peer = self.delivery == "peer" and device.type == "cuda" and self.world > 1
             if peer:
                 try:
@@ -451,6 +453,13 @@ class ColumnShardedGemm:
         """``post(step, **source)`` then ``run(step, out)``."""
         self.post(step, **source)
         return self.run(step, out)
+
+    def forward_slabs(self, out: torch.Tensor, **source) -> torch.Tensor:
+        """The slab pipeline with the step numbering kept here: call k of this method is step k (``plan_slabs`` first).
+        ``source`` as for ``post`` (needed on the root only)."""
+        step = self._next_step
+        self._next_step += 1
+        return self.step(step, out, **source)
 
     def check_rows(self, step: int, out: torch.Tensor, row0: int, rows: int = 128):
         """Recomputes ``rows`` output rows starting at ``row0`` (inside one slab) of this rank's shard with the
