@@ -406,7 +406,7 @@ def main():
     # kernel duration = launches of this one kernel back to back in stream order (the reference's benchmark protocol,
     # gemm_a8w8_blockscale_host.cc:99-121), nothing else running; a launch timed alone on an idle device is reported
     # beside it (it includes the launch latency)
-    reps = max(3, min(20, int(200.0 / max(t_call, 0.1))))
+    reps = max(20, min(400, int(300.0 / max(t_call, 0.1))))       # about 0.3 s of launches: a sustained figure, like the loop's
     for _ in range(3):
         local_gemm()
     torch.cuda.synchronize()
