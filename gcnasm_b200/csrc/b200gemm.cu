@@ -112,7 +112,6 @@ int device_state(DeviceState** out) {
             else
                 cudaGetLastError();
         }
-        CU_TRY(cudaStreamCreateWithFlags(&s.peek_stream, cudaStreamNonBlocking));
         s.init = true;
     }
     *out = &s;
@@ -1219,6 +1218,11 @@ int b200_peek_status(void) {
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc) return rc;
+    {
+        // (created on first use, not with the per-device state: the allocation-free entry point must not create anything)
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!ds->peek_stream) CU_TRY(cudaStreamCreateWithFlags(&ds->peek_stream, cudaStreamNonBlocking));
+    }
     int v = 0;
     CU_TRY(cudaMemcpyAsync(&v, ds->status_ptr, sizeof(int), cudaMemcpyDeviceToHost, ds->peek_stream));
     CU_TRY(cudaStreamSynchronize(ds->peek_stream));
