@@ -78,12 +78,23 @@ static constexpr int kBlockIssuers = 2;
 // Building with -DB200_TRACE records clock64() stamps of the hand-offs of the first CTA pair into g_trace
 // (read back with b200_trace_read); it is how the latencies quoted in the comments here were measured.
 #ifdef B200_TRACE
-// [cta][epilogue warp][phase < 128][4 slots], then the MMA issuer's [phase < 128][4 slots]
-__device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
+// [cta][epilogue warp][phase < 128][8 slots], then the MMA issuer's [phase < 128][8 slots].  Epilogue slots per K group:
+// 7 loop top, 6 accumulator-full barrier passed, 0 first loads issued, 3 first wait::ld done, 4 last load landed,
+// 1 buffer handed back, 5 / 2 the FMAs of the hand-back chunk / of the last chunk have completed (these two read the
+// clock behind a data dependency on the accumulator; a plain clock read does not order against arithmetic)
+// then [phase < 128]: when a polling observer (warp 3 of the leader) saw the group's accumulator-full barrier flip
+__device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8 + 128];
 #define B200_TRACE_EPI(slot)                                                                     \
     do {                                                                                         \
         if (pair_id == 0 && lane == 0 && phase < 128)                                            \
             g_trace[((static_cast<int>(cta) * 8 + ew) * 128 + phase) * 8 + (slot)] = clock64();   \
+    } while (0)
+#define B200_TRACE_EPI_DEP(slot, val)                                                            \
+    do {                                                                                         \
+        long long t_;                                                                            \
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) : "l"(val));                            \
+        if (pair_id == 0 && lane == 0 && phase < 128)                                            \
+            g_trace[((static_cast<int>(cta) * 8 + ew) * 128 + phase) * 8 + (slot)] = t_;         \
     } while (0)
 #define B200_TRACE_MMA(slot)                                                                     \
     do {                                                                                         \
@@ -96,6 +107,7 @@ __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8];
     } while (0)
 #else
 #define B200_TRACE_EPI(slot)
+#define B200_TRACE_EPI_DEP(slot, val)
 #define B200_TRACE_MMA(slot)
 #define B200_TRACE_PROD(slot)
 #endif
@@ -294,6 +306,17 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 }
             }
         }
+#ifdef B200_TRACE
+        else if (MODE == MODE_BLOCK && warp == 3 && lane == 0 && cta == 0 && pair_id == 0) {
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.tiles_total && ok && phase < 128; t += num_pairs)
+                for (int g = 0; g < groups && ok && phase < 128; ++g, ++phase) {
+                    ok = mbar_wait_poll<false, 32>(bar_accf0 + (phase & 1) * 8, (phase >> 1) & 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F);
+                    g_trace[2 * 8 * 128 * 8 + 128 * 8 + phase] = clock64();
+                }
+        }
+#endif
     } else {
         // ---------------------------------- epilogue (both CTAs) ----------------------------------
         setmaxnreg_inc<Cfg::EPI_REGS>();
@@ -351,7 +374,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 float sa_cur = __ldg(sfa_p);
                 float sb0_cur = col_ok ? __ldg(sfb_p) : 0.0f;
                 float sb1_cur = has1 ? __ldg(sfb_p + p.sfb_stride) : 0.0f;
-                // 32-column loads into two register buffers, both in flight at the start; a 16-column tail when
+                // 32-column loads into NB register buffers, all in flight at the start; a 16-column tail when
                 // NCH % 32 != 0.  The TMEM buffer goes back to the MMA issuer as soon as the last load has landed,
                 // before the last FMAs; the next group's scales are fetched after that arrive (an arrive waits for
                 // the thread's outstanding loads).
@@ -359,10 +382,13 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 constexpr int CFULL = NCH / LW, TAIL = NCH % LW;
                 constexpr int NLD = CFULL + (TAIL ? 1 : 0);          // loads per group
                 static_assert(TAIL == 0 || (LW == 32 && TAIL == 16), "tail load is 16 columns");
-                constexpr int REL = (NLD - 1) & ~1;                  // the wait at this chunk covers the final load
+                // register buffers for the loads: with NCH <= 96 the accumulators leave room for every load of a group
+                constexpr int NB = (NCH <= 96 && NLD <= 3) ? NLD : 2;
+                constexpr int REL = ((NLD - 1) / NB) * NB;           // the wait at this chunk covers the final load
                 for (int g = 0; g < groups; ++g, ++phase) {
                     const uint32_t as = phase & 1;
                     const uint32_t aph = (phase >> 1) & 1;
+                    B200_TRACE_EPI(7);
                     if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) {
                         ok = false;
                         break;
@@ -371,38 +397,38 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     tc_fence_after();
                     const uint32_t taddr = taddr0 + as * BN;
                     B200_TRACE_EPI(0);
-                    float v[2][LW];
+                    float v[NB][LW];
                     auto load_chunk = [&](const int c) {
-                        if (c < CFULL) tmem_ld<LW>(taddr + c * LW, v[c & 1]);
-                        else tmem_ld16(taddr + c * LW, v[c & 1]);
+                        if (c < CFULL) tmem_ld<LW>(taddr + c * LW, v[c % NB]);
+                        else tmem_ld16(taddr + c * LW, v[c % NB]);
                     };
-                    load_chunk(0);
-                    if (NLD > 1) load_chunk(1);
+#pragma unroll
+                    for (int c = 0; c < NB && c < NLD; ++c) load_chunk(c);
                     // (only now: the scales were requested during the previous group and may still be on their way; the
                     // multiply that waits for them must not stand between the barrier and the tensor-memory loads)
                     const float s0 = sa_cur * sb0_cur, s1 = kStraddle ? sa_cur * sb1_cur : s0;
                     const unsigned long long sc0 = pack_f32x2(s0, s0), sc1 = kStraddle ? pack_f32x2(s1, s1) : sc0;
-                    // tcgen05.wait::ld waits for every load in flight, so it is executed only before the even
-                    // chunks: an odd chunk landed with its predecessor, and a wait there would stall on the
-                    // refill load issued a moment earlier
+                    // tcgen05.wait::ld waits for every load in flight, so it is executed only before the first chunk
+                    // of each round of NB: the other chunks of the round landed with it, and a wait there would
+                    // stall on the refill load issued a moment earlier
                     auto fma_chunk = [&](const int c) {
                         const unsigned long long scA = (!kStraddle || c * LW < split) ? sc0 : sc1;
                         const unsigned long long scB = (!kStraddle || c * LW + 16 < split) ? sc0 : sc1;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            acc[c * (LW / 2) + j] = ffma2(pack_f32x2(v[c & 1][2 * j], v[c & 1][2 * j + 1]), scA, acc[c * (LW / 2) + j]);
+                            acc[c * (LW / 2) + j] = ffma2(pack_f32x2(v[c % NB][2 * j], v[c % NB][2 * j + 1]), scA, acc[c * (LW / 2) + j]);
                         if constexpr (LW == 32) {
                             if (c < CFULL) {
 #pragma unroll
                                 for (int j = 0; j < 8; ++j)
-                                    acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c & 1][16 + 2 * j], v[c & 1][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
+                                    acc[c * 16 + 8 + j] = ffma2(pack_f32x2(v[c % NB][16 + 2 * j], v[c % NB][16 + 2 * j + 1]), scB, acc[c * 16 + 8 + j]);
                             }
                         }
                     };
 #pragma unroll
                     for (int c = 0; c < NLD; ++c) {
-                        if ((c & 1) == 0) {
-                            tmem_ld_wait();                              // chunks c and c+1 have landed
+                        if (c % NB == 0) {
+                            tmem_ld_wait();                              // chunks c .. c+NB-1 have landed
                             if (c == 0) B200_TRACE_EPI(3);
                         }
                         if (c == REL) {
@@ -410,7 +436,6 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             B200_TRACE_EPI(4);
                             tc_fence_before();
                             __syncwarp();
-                            B200_TRACE_EPI(5);
                             if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
                             B200_TRACE_EPI(1);
                             if (g + 1 < groups) {
@@ -420,10 +445,13 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             }
                         }
                         fma_chunk(c);
+#ifdef B200_TRACE
+                        if (c == REL) B200_TRACE_EPI_DEP(5, acc[(c + 1) * (LW / 2) - 1]);
+                        if (c == NLD - 1) B200_TRACE_EPI_DEP(2, acc[NCH / 2 - 1]);
+#endif
                         // refill the buffer just drained; the load runs behind the next chunk's FMAs
-                        if (c + 2 < NLD) load_chunk(c + 2);
+                        if (c + NB < NLD) load_chunk(c + NB);
                     }
-                    B200_TRACE_EPI(2);
                 }
                 if (!ok) break;
                 if (!c_ordered) {
