@@ -34,7 +34,7 @@ EXPORTS = (
     "b200_fill_uniform", "b200_fill_normal",
     "b200_flag_write", "b200_flag_wait", "b200_stream_copy", "b200_ipc_alloc", "b200_ipc_open", "b200_ipc_close", "b200_ipc_free",
     "b200_slab_bytes", "b200_slab_upload", "b200_last_status", "b200_peek_status", "b200_selftest_bounded_wait", "b200_last_cuda_error", "b200_strerror", "b200_sm_count", "b200_release",
-    "b200_version", "b200_launch_count",
+    "b200_version", "b200_launch_count", "b200_last_tail_split",
 )
 
 
@@ -127,6 +127,7 @@ def lib() -> C.CDLL:
         "b200_release": (i32, []),
         "b200_version": (C.c_char_p, []),
         "b200_launch_count": (u64, []),
+        "b200_last_tail_split": (i32, [vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

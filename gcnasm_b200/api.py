@@ -473,3 +473,11 @@ def peek_status() -> int:
 
 def launch_count() -> int:
     return lib().b200_launch_count()
+
+
+def last_tail_split():
+    """(first split tile, column parts per tile) of this thread's last pair-kernel launch, or None when that launch
+    computed every tile whole."""
+    v = (C.c_int32 * 2)()
+    hit = lib().b200_last_tail_split(C.byref(v, 0), C.byref(v, 4))
+    return (v[0], v[1]) if hit else None

@@ -419,17 +419,56 @@ int max_pairs(Kernel kernel, int threads, int smem, int sm_count) {
     return n < sm_count / 2 ? n : sm_count / 2;
 }
 
+// CTA pairs of this kernel that are resident at once on the current device (0 on failure)
+template <int BN, int MODE, int BL>
+int pair_capacity(int sm_count) {
+    using Cfg = PairCfg<BN, MODE, BL>;
+    auto kernel = gemm_a8w8_pair_sm100_kernel<Cfg>;
+    if (set_smem(kernel, Cfg::SMEM_BYTES)) return 0;
+    static int pairs_cached[kMaxDevices] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDevices) return 0;
+    if (pairs_cached[dev] == 0) pairs_cached[dev] = max_pairs(kernel, Cfg::THREADS, Cfg::SMEM_BYTES, sm_count);
+    return pairs_cached[dev];
+}
+
+// The last round of a persistent schedule is rarely full: 448 tiles on 74 CTA pairs leave 4 tiles for round 7, and 70
+// pairs idle while those are computed.  Block-scale GEMMs on 256 x 256 tiles (row-major B) therefore compute the
+// tiles of a partial last round as 4 (or 2) column parts each, one part per pair, when there are pairs enough: the
+// same K loop with 64- (128-) column MMAs, so every element is summed in exactly the order of a whole tile and
+// nothing meets in memory.  Sets p.tail_first / p.tail_split; B200GEMM_TAIL_SPLIT=0 in the environment (read once)
+// switches it off.
+thread_local int t_last_tail[2] = {0, 0};      // the calling thread's last pair launch (b200_last_tail_split)
+void plan_tail(GemmParams& p, int capacity) {
+    static const bool off = [] {
+        const char* e = std::getenv("B200GEMM_TAIL_SPLIT");
+        return e && *e == '0';
+    }();
+    p.tail_first = p.tiles_total;
+    p.tail_split = 0;
+    if (off || capacity <= 0 || p.kblocks < 4) return;
+    const int full = (p.tiles_total / capacity) * capacity;
+    const int rem = p.tiles_total - full;
+    // (a problem of less than one round is left alone: measured, four times as many pairs on quarter tiles gain nothing there)
+    if (rem == 0 || full == 0) return;
+    const int split = rem * 4 <= capacity ? 4 : (rem * 2 <= capacity ? 2 : 0);
+    if (!split) return;
+    p.tail_first = full;
+    p.tail_split = split;
+    t_last_tail[0] = full;
+    t_last_tail[1] = split;
+}
+
 template <int BN, int MODE, int BL>
 int launch_pair(const GemmParams& p, int sm_count, cudaStream_t st) {
     using Cfg = PairCfg<BN, MODE, BL>;
     auto kernel = gemm_a8w8_pair_sm100_kernel<Cfg>;
-    int rc = set_smem(kernel, Cfg::SMEM_BYTES);
-    if (rc) return rc;
-    static int pairs_cached[kMaxDevices] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (pairs_cached[dev] == 0) pairs_cached[dev] = max_pairs(kernel, Cfg::THREADS, Cfg::SMEM_BYTES, sm_count);
-    const int pairs = p.tiles_total < pairs_cached[dev] ? p.tiles_total : pairs_cached[dev];
+    if (!p.tail_split) t_last_tail[0] = t_last_tail[1] = 0;
+    const int capacity = pair_capacity<BN, MODE, BL>(sm_count);
+    if (capacity <= 0) return B200_ERR_CUDA;
+    int pairs = p.tiles_total < capacity ? p.tiles_total : capacity;
+    if (p.tail_split) pairs = capacity;              // (plan_tail: whole rounds, then one round of parts)
     // programmatic serialization: this launch may begin while its predecessor drains; the kernel decides what it
     // does before the predecessor is complete (b200_gemm_flags)
     cudaLaunchConfig_t cfg;
@@ -686,6 +725,14 @@ int run_gemm(const b200_gemm_args* a, const Plan& pl, DeviceState* ds, cudaStrea
         p.sfb_stride = a->stride_sfb;
         p.sfa_batch = a->stride_sfa_batch;
         p.sfb_batch = a->stride_sfb_batch;
+    }
+    if (pair && BN == 256 && !ab16 && a->scale_mode == B200_SCALE_BLOCK && a->b_layout == B200_B_NK_ROWMAJOR) {
+        plan_tail(p, pair_capacity<256, MODE_BLOCK, BL_NK>(ds->sm_count));
+        if (p.tail_split) {
+            rc = make_rowmajor_tmap(&p.tmap_b_tail, a->ptr_b, a->n, a->k, a->stride_b, b_batches, a->stride_b_batch,
+                                    static_cast<uint32_t>(BROWS / p.tail_split));
+            if (rc) return rc;
+        }
     }
     if (ab16) {
         const bool flat16 = a->b_layout == B200_B_FLAT_16x16;
@@ -1411,5 +1458,10 @@ int b200_trace_read(long long* host, int count) {
 }
 #endif
 uint64_t b200_launch_count(void) { return g_launches.load(); }
+int b200_last_tail_split(int32_t* first_tile, int32_t* parts) {
+    if (first_tile) *first_tile = t_last_tail[0];
+    if (parts) *parts = t_last_tail[1];
+    return t_last_tail[1] > 0 ? 1 : 0;
+}
 
 }  // extern "C"

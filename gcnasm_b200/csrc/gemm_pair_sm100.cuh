@@ -14,6 +14,8 @@
 // between two TMEM buffers and are folded into register accumulators with packed fp32 FMAs.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_sm100.cuh"
 
 namespace b200 {
@@ -174,6 +176,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
 
     const int groups = (MODE == MODE_BLOCK) ? p.kblocks : 1;
     const int kb_per_group = (MODE == MODE_BLOCK) ? 1 : p.kblocks;
+    // work units: whole tiles, then (block-scale, when the launcher set it up) the column parts of the tail tiles
+    constexpr bool kTail = (MODE == MODE_BLOCK) && BN == 256 && Cfg::BLAYOUT == BL_NK;
+    const int units_total = (kTail && p.tail_split) ? p.tail_first + (p.tiles_total - p.tail_first) * p.tail_split
+                                                    : p.tiles_total;
     // Unless the caller vouched for the operands, nothing is read or written before the previous kernel is complete.
     // With inputs_ready only the writes to C wait (in the epilogue, before the first tile is stored).
     if (!p.inputs_ready) pdl_wait();
@@ -188,7 +194,9 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             bool ok = true;
             int ready_b = -1;                         // last batch whose ready word has been seen
             const uint32_t leader_full0 = mapa_shared(bar_full0, 0);
-            for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
+            for (int u = pair_id; u < units_total && ok; u += num_pairs) {
+                int t = u, part = -1;
+                if constexpr (kTail) unit_coords(p, u, t, part);
                 int b, mi, ni;
                 tile_coords(p, t, b, mi, ni);
                 if (p.batch_ready && b != ready_b) {
@@ -198,7 +206,10 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 }
                 const int bq = p.b_shared ? 0 : b;    // batch coordinate of the weights
                 const int row_a = mi * (2 * BM) + static_cast<int>(cta) * BM;
-                const int row_b = ni * BN + static_cast<int>(cta) * BH;
+                // a column part of a tail tile takes BH / tail_split rows of B per CTA, through the narrower box
+                const int sub_rows = (kTail && part >= 0) ? BH / p.tail_split : BH;
+                const int row_b = ni * BN + ((kTail && part >= 0) ? part * 2 * sub_rows : 0) + static_cast<int>(cta) * sub_rows;
+                const CUtensorMap* tmap_b_u = (kTail && part >= 0) ? &p.tmap_b_tail : &p.tmap_b;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -211,11 +222,11 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                     B200_TRACE_PROD(0);
                     if (cta == 0)
                         mbar_arrive_expect_tx(bar_full0 + s * 8,
-                                              2 * (Cfg::A_BYTES + Cfg::B_BYTES + Cfg::SFA_BYTES + Cfg::SFB_BYTES));
+                                              2 * (Cfg::A_BYTES + sub_rows * BK + Cfg::SFA_BYTES + Cfg::SFB_BYTES));
                     const uint32_t full = leader_full0 + s * 8;
                     tma_load_3d_pair(sa, &p.tmap_a, full, kb * BK, row_a, b);
                     if constexpr (Cfg::BLAYOUT == BL_NK)
-                        tma_load_3d_pair(sb, &p.tmap_b, full, kb * BK, row_b, bq);
+                        tma_load_3d_pair(sb, tmap_b_u, full, kb * BK, row_b, bq);
                     else
                         tma_load_4d_pair(sb, &p.tmap_b, full, 0, row_b / 16, kb * (BK / 16), bq);
                     B200_TRACE_PROD(1);
@@ -240,15 +251,23 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             uint32_t it = 0, phase = 0;
             bool ok = true;
             constexpr uint32_t idesc = make_idesc_f8(2 * BM, BN);
-            for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
-                for (int g = 0; g < groups && ok; ++g, ++phase) {
+            for (int u = pair_id; u < units_total && ok; u += num_pairs) {
+                // A column part of a tail tile: the same K loop with a narrower instruction, and tail_split K groups per
+                // accumulator hand-off -- their partial sums lie side by side in the 256-column buffer (4 x 64 or 2 x 128).
+                const bool tail_u = kTail && p.tail_split && u >= p.tail_first;
+                const uint32_t idesc_u = tail_u ? make_idesc_f8(2 * BM, BN / p.tail_split) : idesc;
+                const int gp = tail_u ? p.tail_split : 1;
+                const uint32_t nsub = tail_u ? static_cast<uint32_t>(BN / p.tail_split) : 0u;
+                for (int g = 0; g < groups && ok; g += gp, ++phase) {
+                    const int cnt = (groups - g) < gp ? (groups - g) : gp;
                     if (kIssuers > 1 && (phase % kIssuers) != my_slot) {
-                        it += kb_per_group;           // another issuer's group
+                        it += cnt * kb_per_group;     // another issuer's hand-off
                         continue;
                     }
                     const uint32_t as = phase % ACC_STAGES;
                     const uint32_t aph = (phase / ACC_STAGES) & 1;
-                    const uint32_t tacc = tmem_base + as * BN;
+                    for (int j = 0; j < cnt && ok; ++j) {
+                    const uint32_t tacc = tmem_base + as * BN + j * nsub;
                     for (int kb = 0; kb < kb_per_group; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
@@ -258,7 +277,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                             ok = false;
                             break;
                         }
-                        if (kb == 0) {
+                        if (kb == 0 && j == 0) {
                             B200_TRACE_MMA(0);
                             if (!B200_MMA_WAIT(bar_acce0 + as * 8, aph ^ 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_E)) {
                                 ok = false;
@@ -294,12 +313,13 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                                 umma_mxf8<2>(tacc, da, db, make_idesc_mxf8(2 * BM, BN, k, k), accum, tsf, tsf + 4);
                             } else {
                                 if constexpr (Cfg::AB16) umma_f16<2>(tacc, da, db, make_idesc_bf16(2 * BM, BN), accum);
-                                else umma_f8<2>(tacc, da, db, idesc, accum);
+                                else umma_f8<2>(tacc, da, db, idesc_u, accum);
                             }
                         }
                         B200_TRACE_MMA(4);
                         umma_commit_pair(bar_empty0 + s * 8);       // frees stage s in both CTAs
                         B200_TRACE_MMA(5);
+                    }
                     }
                     if (ok) umma_commit_pair(bar_accf0 + as * 8);   // wakes the epilogues of both CTAs
                     B200_TRACE_MMA(3);
@@ -310,7 +330,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         else if (MODE == MODE_BLOCK && warp == 3 && lane == 0 && cta == 0 && pair_id == 0) {
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = pair_id; t < p.tiles_total && ok && phase < 128; t += num_pairs)
+            for (int u = pair_id; u < units_total && ok && phase < 128; u += num_pairs)
                 for (int g = 0; g < groups && ok && phase < 128; ++g, ++phase) {
                     ok = mbar_wait_poll<false, 32>(bar_accf0 + (phase & 1) * 8, (phase >> 1) & 1, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F);
                     g_trace[2 * 8 * 128 * 8 + 128 * 8 + phase] = clock64();
@@ -338,12 +358,112 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         }
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = pair_id; t < p.tiles_total && ok; t += num_pairs) {
+        // One column part of a tail tile: NC 32-column chunks per thread and K group (the part is 64 * NC columns wide;
+        // the half-0 warps take its first 32 * NC columns, the half-1 warps the rest).  The MMA issuer puts GP = 4 / NC
+        // K groups side by side into one 256-column buffer per hand-off, so a hand-off brings four chunks per thread,
+        // all loaded at once, each scaled with its own group's scales into the same accumulators.  The result leaves
+        // through the per-warp staging buffer.
+        auto tail_unit = [&](auto nc_tag, const int b, const int mi, const int ni, const int part) -> bool {
+            constexpr int NC = decltype(nc_tag)::value;
+            constexpr int CW = NC * 32, GP = 4 / NC;
+            unsigned long long acc_t[CW / 2];
+#pragma unroll
+            for (int j = 0; j < CW / 2; ++j) acc_t[j] = 0ull;
+            const int row = mi * (2 * BM) + row_in_tile;
+            const int col_first = ni * BN + part * (2 * CW) + half * CW;
+            const bool col_ok = col_first < p.n;
+            const float* sfa_p = p.sfa + b * p.sfa_batch + (row < p.m ? row : 0);
+            const float* sfb_p = p.sfb + b * p.sfb_batch + static_cast<long long>(col_first >> 7) * p.sfb_stride;
+            const uint32_t taddr0 = tmem_base + tmem_lane + half * CW;
+            float sa_c[GP], sb_c[GP];
+            auto load_scales = [&](const int g0) {
+#pragma unroll
+                for (int j = 0; j < GP; ++j) {
+                    const int g = (g0 + j < groups) ? g0 + j : groups - 1;
+                    sa_c[j] = __ldg(sfa_p + static_cast<long long>(g) * p.sfa_stride);
+                    sb_c[j] = col_ok ? __ldg(sfb_p + g) : 0.0f;
+                }
+            };
+            load_scales(0);
+            for (int g0 = 0; g0 < groups; g0 += GP, ++phase) {
+                const int cnt = (groups - g0) < GP ? (groups - g0) : GP;
+                const uint32_t as = phase & 1;
+                const uint32_t aph = (phase >> 1) & 1;
+                if (!B200_EPI_WAIT(bar_accf0 + as * 8, aph, abort_flag, p.status, KSTAT_TIMEOUT_ACC_F)) return false;
+                tc_fence_after();
+                unsigned long long sc2[GP];
+#pragma unroll
+                for (int j = 0; j < GP; ++j) {
+                    const float sc = sa_c[j] * sb_c[j];
+                    sc2[j] = pack_f32x2(sc, sc);
+                }
+                // the four chunks q = j * NC + c of this hand-off in two rounds of two (two 32-column register buffers,
+                // as in the whole-tile loop); the buffer goes back once the second round has landed
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float v[2][32];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        // (loaded whether or not group j exists in this hand-off: a conditional load would keep the
+                        // buffer's old contents alive; what it brings for a missing group is never used)
+                        const int q = 2 * r + h, j = q / NC, c = q % NC;
+                        tmem_ld<32>(taddr0 + as * BN + j * (2 * CW) + c * 32, v[h]);
+                    }
+                    tmem_ld_wait();
+                    if (r == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_acce0 + as * 8);
+                        if (g0 + GP < groups) load_scales(g0 + GP);
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int q = 2 * r + h, j = q / NC, c = q % NC;
+                        if (j < cnt) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                acc_t[c * 16 + i] = ffma2(pack_f32x2(v[h][2 * i], v[h][2 * i + 1]), sc2[j], acc_t[c * 16 + i]);
+                        }
+                    }
+                }
+            }
+            if (!c_ordered) {
+                pdl_wait();
+                c_ordered = true;
+            }
+            if (stores_pending) {
+                // the staging buffer lies inside the area the previous tile's bulk stores are reading
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+                stores_pending = false;
+            }
+            const int row0 = row - lane;
+            uint8_t* cbatch = reinterpret_cast<uint8_t*>(p.c) + static_cast<size_t>(b) * p.c_batch * esz;
+            uint8_t* out_stage = smem_gen + STAGES * Cfg::STAGE_BYTES + 1024 +
+                                 (Cfg::TILE_TMA ? ew * (32 * NCH * 2) : ew * kOutStageBytesPerWarp);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                float o[32];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) unpack_f32x2(acc_t[c * 16 + j], o[2 * j], o[2 * j + 1]);
+                if (p.out_dtype == OUT_BF16) {
+                    store_chunk_coalesced<32>(p, cbatch, out_stage, row0, col_first + c * 32, o, lane, vec_ok);
+                } else {
+                    store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_first + c * 32, o, lane, vec_ok);
+                    store_chunk_coalesced<16>(p, cbatch, out_stage, row0, col_first + c * 32 + 16, o + 16, lane, vec_ok);
+                }
+            }
+            return true;
+        };
+        for (int u = pair_id; u < units_total && ok; u += num_pairs) {
+            int t = u, part = -1;
+            if constexpr (kTail) unit_coords(p, u, t, part);
             int b, mi, ni;
             tile_coords(p, t, b, mi, ni);
-            // (first tile of this pair in batch b; recomputed from t so that no state stays live across the K loop)
+            // (first unit of this pair in batch b; recomputed from u so that no state stays live across the K loop.  The
+            // unit before, u - num_pairs, is always a whole tile: the column parts are the last round.)
             if (MODE == MODE_BLOCK && p.batch_ready &&
-                (t < num_pairs || (t - num_pairs) / (p.tiles_m * p.tiles_n) != b)) {
+                (u < num_pairs || (u - num_pairs) / (p.tiles_m * p.tiles_n) != b)) {
                 // the A scales of this batch travel with its slab: they are read below, possibly long before the
                 // producer's first load of the tile, so the epilogue warps look at the ready word themselves
                 int seen = 1;
@@ -357,6 +477,17 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             const int row = mi * (2 * BM) + row_in_tile;
 
             if constexpr (MODE == MODE_BLOCK) {
+                if constexpr (kTail) {
+                    if (part >= 0) {
+                        const bool fine = (p.tail_split == 4) ? tail_unit(std::integral_constant<int, 1>{}, b, mi, ni, part)
+                                                              : tail_unit(std::integral_constant<int, 2>{}, b, mi, ni, part);
+                        if (!fine) {
+                            ok = false;
+                            break;
+                        }
+                        continue;
+                    }
+                }
                 unsigned long long acc[NCH / 2];
 #pragma unroll
                 for (int j = 0; j < NCH / 2; ++j) acc[j] = 0ull;
@@ -461,7 +592,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
                 // Everything the store phase needs is derived again from the tile index here, behind an opaque copy of
                 // it: nothing of it then has to stay in a register across the K loop, where the accumulators and the two
                 // load buffers leave none to spare.
-                int t_s = t, ew_s = ew;
+                int t_s = u, ew_s = ew;                                // (a whole tile here: its unit index is its tile index)
                 uint32_t sb_s = smem_base;
                 asm volatile("" : "+r"(t_s), "+r"(ew_s), "+r"(sb_s));
                 uint8_t* smem_gen_s = smem_raw + (sb_s - smem_u32(smem_raw));

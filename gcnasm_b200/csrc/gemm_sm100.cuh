@@ -46,8 +46,26 @@ struct GemmParams {
     int b_shared;                // pair kernels: every batch multiplies by the same B (B is read at batch coordinate 0)
     int batch_epoch;             // pair kernels: value a batch's ready word must have reached (with batch_ready)
     const int* batch_ready;      // pair kernels: one ready word per batch, or null
+    // pair kernels, block-scale, 256 x 256 tiles, row-major B: the tiles from tail_first on (the last, partly filled
+    // round of the persistent schedule) are each computed as tail_split (2 or 4) column parts of 256 / tail_split
+    // columns by as many CTA pairs -- narrower MMAs over the full K, so every output element is summed exactly as in a
+    // whole tile.  tmap_b_tail is B with a box of 128 / tail_split rows.  tail_split == 0: whole tiles only.
+    CUtensorMap tmap_b_tail;
+    int tail_first, tail_split;
     int* status;
 };
+
+// Work unit u of a pair kernel -> its tile and column part (part < 0: the whole tile).
+__device__ __forceinline__ void unit_coords(const GemmParams& p, int u, int& t, int& part) {
+    if (p.tail_split == 0 || u < p.tail_first) {
+        t = u;
+        part = -1;
+    } else {
+        const int r = u - p.tail_first;
+        t = p.tail_first + r / p.tail_split;
+        part = r - (t - p.tail_first) * p.tail_split;
+    }
+}
 
 template <int BN_, int MODE_, int BLAYOUT_>
 struct GemmCfg {

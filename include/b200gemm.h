@@ -115,6 +115,15 @@ int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream);
  * into a CUDA graph (an allocation cannot happen inside a capture, and a captured launch keeps the pointer it was
  * given); and do not call b200_release while captured graphs that contain these launches are still replayed.      */
 
+/* Tail of a block-scale GEMM.  The kernels are persistent: CTA pairs take tiles round by round, and the last round is
+ * rarely full (448 tiles of 256 x 256 on 74 pairs: 4 tiles in round 7, 70 pairs idle meanwhile).  With row-major B
+ * and 256 x 256 tiles the tiles of a partial last round that follows at least one whole round are each computed as 4
+ * (or 2) column parts by as many pairs, when there are pairs enough for all parts: narrower MMAs over the full K, every element summed in the order of a
+ * whole tile -- results do not depend on whether a tile was split.  B200GEMM_TAIL_SPLIT=0 in the environment (read
+ * once) switches this off.  b200_last_tail_split reports what the calling thread's last pair-kernel launch did:
+ * returns 1 and the first split tile and the parts per tile, or 0.                                              */
+int b200_last_tail_split(int32_t* first_tile, int32_t* parts);
+
 /* Validates `args` exactly as b200_gemm_a8w8 would, without touching the GPU. Also reports the tile
  * configuration the launcher would pick (a b200_tile_hint value) when `chosen_tile` is not null.        */
 int b200_gemm_check(const b200_gemm_args* args, int32_t* chosen_tile);
