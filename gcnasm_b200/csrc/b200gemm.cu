@@ -433,7 +433,7 @@ int pair_capacity(int sm_count) {
     return pairs_cached[dev];
 }
 
-// The last round of a persistent schedule is rarely full: 448 tiles on 74 CTA pairs leave 4 tiles for round 7, and 70
+// The last round of a persistent schedule is rarely full: 448 tiles on 74 CTA pairs leave 4 tiles for a seventh round, and 70
 // pairs idle while those are computed.  Block-scale GEMMs on 256 x 256 tiles (row-major B) therefore compute the
 // tiles of a partial last round as 4 (or 2) column parts each, one part per pair, when there are pairs enough: the
 // same K loop with 64- (128-) column MMAs, so every element is summed in exactly the order of a whole tile and

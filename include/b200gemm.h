@@ -116,7 +116,7 @@ int b200_gemm_a8w8(const b200_gemm_args* args, void* cuda_stream);
  * given); and do not call b200_release while captured graphs that contain these launches are still replayed.      */
 
 /* Tail of a block-scale GEMM.  The kernels are persistent: CTA pairs take tiles round by round, and the last round is
- * rarely full (448 tiles of 256 x 256 on 74 pairs: 4 tiles in round 7, 70 pairs idle meanwhile).  With row-major B
+ * rarely full (448 tiles of 256 x 256 on 74 pairs: a seventh round of 4 tiles, 70 pairs idle meanwhile).  With row-major B
  * and 256 x 256 tiles the tiles of a partial last round that follows at least one whole round are each computed as 4
  * (or 2) column parts by as many pairs, when there are pairs enough for all parts: narrower MMAs over the full K, every element summed in the order of a
  * whole tile -- results do not depend on whether a tile was split.  B200GEMM_TAIL_SPLIT=0 in the environment (read
