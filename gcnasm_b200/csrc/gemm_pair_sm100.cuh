@@ -76,6 +76,9 @@ struct PairCfg {
 // UMMA issuer threads in block-scale mode (warps 1..kBlockIssuers of the leader CTA); at most the number of
 // TMEM buffers, because an issuer has to observe every phase of the barriers it waits on.
 static constexpr int kBlockIssuers = 2;
+// The TMA producer thread sits on the scheduler that hosts no issuer (warps 1..2 issue, warp w runs on scheduler w % 4):
+// measured against warp 0, 1.5-2 % on the 4096 x 7168 x 2048 and 16384 x 7168 x 8192 problems, nothing on 8192^3.
+static constexpr int kProducerWarp = 3;
 
 // Building with -DB200_TRACE records clock64() stamps of the hand-offs of the first CTA pair into g_trace
 // (read back with b200_trace_read); it is how the latencies quoted in the comments here were measured.
@@ -84,7 +87,7 @@ static constexpr int kBlockIssuers = 2;
 // 7 loop top, 6 accumulator-full barrier passed, 0 first loads issued, 3 first wait::ld done, 4 last load landed,
 // 1 buffer handed back, 5 / 2 the FMAs of the hand-back chunk / of the last chunk have completed (these two read the
 // clock behind a data dependency on the accumulator; a plain clock read does not order against arithmetic)
-// then [phase < 128]: when a polling observer (warp 3 of the leader) saw the group's accumulator-full barrier flip
+// then [phase < 128]: when a polling observer (warp 0 of the leader) saw the group's accumulator-full barrier flip
 __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8 + 128];
 #define B200_TRACE_EPI(slot)                                                                     \
     do {                                                                                         \
@@ -105,7 +108,7 @@ __device__ long long g_trace[2 * 8 * 128 * 8 + 128 * 8 + 128];
 // the producers' stamps share the issuer rows: slots 6 and 7 of row it (leader CTA only)
 #define B200_TRACE_PROD(slot)                                                                    \
     do {                                                                                         \
-        if (pair_id == 0 && cta == 0 && warp == 0 && it < 128) g_trace[2 * 8 * 128 * 8 + it * 8 + 6 + (slot)] = clock64(); \
+        if (pair_id == 0 && cta == 0 && warp == kProducerWarp && it < 128) g_trace[2 * 8 * 128 * 8 + it * 8 + 6 + (slot)] = clock64(); \
     } while (0)
 #else
 #define B200_TRACE_EPI(slot)
@@ -188,7 +191,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
         // fall through to the teardown
     } else if (warp < 4) {
         setmaxnreg_dec<Cfg::ROLE_REGS>();
-        if (warp == 0 && lane == 0) {
+        if (warp == kProducerWarp && lane == 0) {
             // ------------------------------ TMA producer (both CTAs) ------------------------------
             uint32_t it = 0;
             bool ok = true;
@@ -327,7 +330,7 @@ gemm_a8w8_pair_sm100_kernel(const __grid_constant__ GemmParams p) {
             }
         }
 #ifdef B200_TRACE
-        else if (MODE == MODE_BLOCK && warp == 3 && lane == 0 && cta == 0 && pair_id == 0) {
+        else if (MODE == MODE_BLOCK && warp == 0 && lane == 0 && cta == 0 && pair_id == 0) {
             uint32_t phase = 0;
             bool ok = true;
             for (int u = pair_id; u < units_total && ok && phase < 128; u += num_pairs)
