@@ -334,14 +334,17 @@ def main():
         op.run(i, outs[i % 2])
         state["next"] = i + 1
 
-    def one_call_ms():
+    def one_call_ms(burst=8):
+        # steady-state time of a call (a burst back to back): a single call on an idle device shows its whole delivery
+        # and would make the timed region come out shorter than asked for
         torch.cuda.synchronize()
         e0, e1 = ev(), ev()
         e0.record()
-        call()
+        for _ in range(burst):
+            call()
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
+        return e0.elapsed_time(e1) / burst
 
     call()
     call()
