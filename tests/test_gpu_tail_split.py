@@ -100,3 +100,34 @@ def test_batched_shared_b_with_tail(api, O):
     done(api)
     for i in range(B):
         assert_close(O, c[i], O.gemm_ref_blockscale(a[i], b, sfa[i], sfb), f"slab {i}")
+
+
+def test_ragged_columns_and_strided_output(api, O):
+    """N = 2176 leaves the last tile column with 128 valid columns (parts 2 and 3 of its tiles lie outside the matrix);
+    the output is a view with a row pitch that is not a multiple of 16 bytes, so the parts take the scalar store path."""
+    m, n, k = 2560, 2176, 512
+    a, b, sfa, sfb = inputs(O, m, n, k, 41)
+    ref = O.gemm_ref_blockscale(a, b, sfa, sfb)
+    c = api.gemm_a8w8_blockscale(T(a), T(b), T(sfa), T(sfb), out_dtype=torch.float32, tile=4)
+    assert api.last_tail_split() == expected_plan(api, m, n)
+    done(api)
+    assert_close(O, c.cpu().numpy(), ref, "ragged columns")
+    wide = torch.full((m, n + 3), -7.0, dtype=torch.float32, device=DEV)
+    api.gemm_a8w8_blockscale(T(a), T(b), T(sfa), T(sfb), out=wide[:, :n], tile=4)
+    done(api)
+    assert torch.equal(wide[:, :n], c) and torch.all(wide[:, n:] == -7.0)
+
+
+def test_overlapped_launches_with_tail(api, O):
+    """B200_GEMM_INPUTS_READY chains: launches that start while their predecessor drains, each with a split tail, writing
+    the same C -- the last one wins, and nothing changes against launches in plain order."""
+    m, n, k = 2560, 2048, 512
+    sets = [[T(x) for x in inputs(O, m, n, k, 50 + j)] for j in range(3)]
+    want = [api.gemm_a8w8_blockscale(*s, out_dtype=torch.bfloat16, tile=4) for s in sets]
+    done(api)
+    shared = torch.empty_like(want[0])
+    for _ in range(3):
+        for s in sets:
+            api.gemm_a8w8_blockscale(*s, out=shared, tile=4, inputs_ready=True)
+    done(api)
+    assert torch.equal(shared, want[2])
